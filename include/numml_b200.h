@@ -1,0 +1,122 @@
+/*
+ * numml_b200 -- C ABI of the sm_100a differentiable-CSR kernels.
+ *
+ * This is the drop-in boundary underneath the operator functions that the reference registers
+ * in its `numml_torch_cpp` extension module (reference cpp/sparse_csr.cpp:307-319, prototypes in
+ * cpp/sparse_csr.hpp:32-105).  Every entry point takes plain device pointers and sizes, a CUDA
+ * stream as an opaque pointer, and returns an `nb200_status`; nothing here depends on torch.
+ *
+ * Conventions
+ *   - matrices are CSR: data[nnz] (float or double), indices[nnz], indptr[rows+1]; index arrays
+ *     are int32 or int64 as selected by `itype` (the reference stores int64; a narrowed int32
+ *     copy halves the index traffic and is what the host layer caches per sparsity pattern);
+ *   - `dtype` is an nb200_dtype, `itype` an nb200_itype;
+ *   - all pointers are device pointers on the current device unless stated otherwise; data,
+ *     indices and the nnz-sized outputs must be 16-byte aligned (128-bit loads and stores);
+ *   - inputs are borrowed and never written; outputs and workspaces are caller-allocated, the
+ *     library allocates no device memory; every call is asynchronous on `stream`;
+ *   - columns within a row are expected in ascending order wherever the reference expects it
+ *     (SpGEMM backward, triangular solve).
+ */
+#ifndef NUMML_B200_H_
+#define NUMML_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    NB200_OK = 0,
+    NB200_ERR_BAD_ARG = 1,      /* null pointer, negative size, unknown dtype / itype            */
+    NB200_ERR_ALIGN = 2,        /* a pointer that must be 16-byte aligned is not                 */
+    NB200_ERR_TOO_LARGE = 3,    /* a size exceeds what the index width / kernel supports         */
+    NB200_ERR_PRECONDITION = 4, /* structural precondition violated (reported via status word)   */
+    NB200_ERR_WAIT_BUDGET = 5,  /* a bounded device-side wait ran out (reported via status word) */
+    NB200_ERR_WORKSPACE = 6,    /* workspace too small                                           */
+    NB200_ERR_CUDA = 7          /* a CUDA runtime call or launch failed                          */
+} nb200_status;
+
+typedef enum { NB200_F32 = 0, NB200_F64 = 1 } nb200_dtype;
+typedef enum { NB200_I32 = 0, NB200_I64 = 1 } nb200_itype;
+
+typedef void* nb200_stream; /* a cudaStream_t */
+
+#if defined(__GNUC__)
+#define NB200_API __attribute__((visibility("default")))
+#else
+#define NB200_API
+#endif
+
+/* Library version (major*10000 + minor*100 + patch) and a printable name for a status. */
+NB200_API int nb200_version(void);
+NB200_API const char* nb200_status_string(int status);
+
+/* ---------------------------------------------------------------------------------------------
+ * SpMV forward  y = A x.          Replaces spgemv_forward (reference cpp/sparse_csr.hpp:32-36,
+ * CPU cpp/sparse_csr_cpu.cpp:11-39, CUDA cpp/sparse_csr_cuda.cu:21-67).
+ * Rows are summed in storage order with an unfused multiply and add, so for matrices taken by
+ * the row-streaming kernel (mean row length <= 24) the result is bit-identical to the reference
+ * CPU loop.  `perm` (itype, may be NULL): when given, entry k uses data[perm[k]] -- this is how
+ * a cached transposed structure is applied to the current values (y = A^T g).
+ * ------------------------------------------------------------------------------------------- */
+NB200_API int nb200_spgemv_forward(int64_t rows, int64_t cols, int64_t nnz,
+                         const void* data, const void* indices, const void* indptr,
+                         const void* perm, const void* x, void* y,
+                         int dtype, int itype, nb200_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * SpMV backward.                  Replaces spgemv_backward (reference cpp/sparse_csr.hpp:38-42,
+ * CPU cpp/sparse_csr_cpu.cpp:41-77, CUDA cpp/sparse_csr_cuda.cu:76-170).
+ *   grad_A[k] = g[row(k)] * x[col(k)]        (always; bit-identical to the reference)
+ *   grad_x    = A^T g
+ * With a transposed structure (t_indptr[cols+1], t_indices[nnz] = row of each entry of A^T,
+ * t_perm[nnz] = position in A of each entry of A^T; see nb200_csr_transpose_structure) grad_x is
+ * a gather over A^T: atomic-free, deterministic and bit-identical to the reference.  With the
+ * three t_* pointers NULL grad_x is zeroed and accumulated with floating-point atomics in one
+ * fused pass over A (order of additions not fixed).
+ * ------------------------------------------------------------------------------------------- */
+NB200_API int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
+                          const void* data, const void* indices, const void* indptr,
+                          const void* x, const void* g,
+                          const void* t_indptr, const void* t_indices, const void* t_perm,
+                          void* grad_A, void* grad_x,
+                          int dtype, int itype, nb200_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * CSR transpose (structure).      Replaces csr_transpose_forward (reference
+ * cpp/sparse_csr.hpp:57-60, CPU cpp/sparse_csr_cpu.cpp:311-367, CUDA cpp/sparse_csr_cuda.cu:176-279).
+ * Stable counting/radix sort of the entries by column: t_indptr[cols+1], t_indices[nnz] (row of
+ * each entry of A^T, ascending within a row of A^T) and t_perm[nnz] (the reference's
+ * At_to_A_idx).  Outputs are written with index width `itype_out`.  Values follow with
+ * nb200_gather(t_data = data[t_perm]).  Needs nnz < 2^31 and rows, cols < 2^31.
+ * `workspace` must hold nb200_csr_transpose_workspace_bytes(rows, cols, nnz) bytes.
+ * ------------------------------------------------------------------------------------------- */
+NB200_API size_t nb200_csr_transpose_workspace_bytes(int64_t rows, int64_t cols, int64_t nnz);
+NB200_API int nb200_csr_transpose_structure(int64_t rows, int64_t cols, int64_t nnz,
+                                  const void* indices, const void* indptr, int itype_in,
+                                  void* t_indptr, void* t_indices, void* t_perm, int itype_out,
+                                  void* workspace, size_t workspace_bytes, nb200_stream stream);
+
+/* dst[k] = src[idx[k]]  (k < n).  With nb200_csr_transpose_structure this completes
+ * csr_transpose_forward (At_data = A_data[At_to_A_idx]). */
+NB200_API int nb200_gather(int64_t n, const void* src, const void* idx, void* dst,
+                 int dtype, int itype, nb200_stream stream);
+
+/* dst[idx[k]] = src[k]  (k < n).  Replaces csr_transpose_backward (reference
+ * cpp/sparse_csr.hpp:62-64, CPU cpp/sparse_csr_cpu.cpp:369-385, CUDA cpp/sparse_csr_cuda.cu:281-295). */
+NB200_API int nb200_scatter(int64_t n, const void* src, const void* idx, void* dst,
+                  int dtype, int itype, nb200_stream stream);
+
+/* out32[k] = (int32) in64[k] and out64[k] = in32[k]: index-width conversion used when the host
+ * layer builds its cached int32 copy of a pattern (the reference stores int64 everywhere,
+ * numml/sparse/_csr.py:599-600,626-639). */
+NB200_API int nb200_narrow_indices(int64_t n, const int64_t* in64, int32_t* out32, nb200_stream stream);
+NB200_API int nb200_widen_indices(int64_t n, const int32_t* in32, int64_t* out64, nb200_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NUMML_B200_H_ */

@@ -1,0 +1,69 @@
+"""ctypes binding of ``libnumml_b200.so`` (the C ABI declared in ``include/numml_b200.h``).
+
+The library is the only compute path of this package: if it is missing, loading fails with an
+error instead of falling back to anything else.
+"""
+import ctypes
+import os
+
+from . import build as _build
+
+_c = ctypes
+_i64, _int, _vp, _sz = _c.c_int64, _c.c_int, _c.c_void_p, _c.c_size_t
+
+F32, F64 = 0, 1
+I32, I64 = 0, 1
+
+# name -> (restype, argtypes); mirrors include/numml_b200.h one to one
+SIGNATURES = {
+    "nb200_version": (_int, []),
+    "nb200_status_string": (_c.c_char_p, [_int]),
+    "nb200_spgemv_forward": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
+    "nb200_spgemv_backward": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
+    "nb200_csr_transpose_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "nb200_csr_transpose_structure": (_int, [_i64, _i64, _i64, _vp, _vp, _int, _vp, _vp, _vp, _int, _vp, _sz, _vp]),
+    "nb200_gather": (_int, [_i64, _vp, _vp, _vp, _int, _int, _vp]),
+    "nb200_scatter": (_int, [_i64, _vp, _vp, _vp, _int, _int, _vp]),
+    "nb200_narrow_indices": (_int, [_i64, _vp, _vp, _vp]),
+    "nb200_widen_indices": (_int, [_i64, _vp, _vp, _vp]),
+}
+
+_lib = None
+
+
+class NB200Error(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, fn, status, text):
+        super().__init__(f"{fn} failed: status {status} ({text})")
+        self.status = status
+
+
+def library_path():
+    return _build.LIB_PATH
+
+
+def lib():
+    """Load the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"{path} is missing: the CUDA library of numml_b200 has not been built "
+                "(run `python -m numml_b200.build`); there is no fallback path.")
+        handle = ctypes.CDLL(path)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError if the symbol is not exported
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def call(name, *args):
+    """Call an int-status entry point and raise NB200Error on failure."""
+    handle = lib()
+    status = getattr(handle, name)(*args)
+    if status != 0:
+        raise NB200Error(name, status, handle.nb200_status_string(status).decode())

@@ -1,0 +1,101 @@
+"""Per-sparsity-pattern plans: what can be computed once from ``(indices, indptr)`` and reused
+while the values change (CG iterations, training steps).
+
+A plan holds
+  * int32 copies of ``indices`` / ``indptr`` (the reference stores int64 everywhere,
+    reference ``numml/sparse/_csr.py:599-600,626-639``; the kernels read half the index bytes from
+    the narrowed copy) -- only when nnz, rows and cols fit in 31 bits;
+  * the transposed structure (``t_indptr``, ``t_indices``, ``t_perm``), built on first use.
+
+Plans are looked up by the identity of the two index tensors (storage pointer, length, in-place
+version counter).  A cache entry keeps the tensors alive, so a pointer can never be recycled
+for a different pattern while its entry exists; an in-place edit bumps the version and misses.
+"""
+import collections
+import ctypes
+
+import torch
+
+from . import _cabi
+
+_INT32_MAX = 2 ** 31 - 1
+_CACHE = collections.OrderedDict()
+_CACHE_SIZE = 8
+force_int64 = False  # set True to make every kernel read the int64 arrays as stored (measurement aid)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr() if t is not None and t.numel() > 0 else 0)
+
+
+class PatternPlan:
+    def __init__(self, rows, cols, indices, indptr):
+        self.rows, self.cols = int(rows), int(cols)
+        self.indices, self.indptr = indices, indptr
+        self.nnz = int(indices.numel())
+        self.version = (indices._version, indptr._version)
+        self._narrow = None
+        self._t = None
+        self.extra = {}
+
+    # -- index-width selection -------------------------------------------------------------
+    def fits_int32(self):
+        return (not force_int64) and max(self.nnz, self.rows, self.cols) < _INT32_MAX
+
+    def csr(self):
+        """(indices, indptr, itype) in the width the kernels should read."""
+        if not self.fits_int32():
+            return self.indices, self.indptr, _cabi.I64
+        if self._narrow is None:
+            with torch.cuda.device(self.indices.device):
+                i32 = torch.empty(self.nnz, dtype=torch.int32, device=self.indices.device)
+                p32 = torch.empty(self.rows + 1, dtype=torch.int32, device=self.indices.device)
+                _cabi.call("nb200_narrow_indices", self.nnz, _ptr(self.indices), _ptr(i32), _stream())
+                _cabi.call("nb200_narrow_indices", self.rows + 1, _ptr(self.indptr), _ptr(p32), _stream())
+            self._narrow = (i32, p32)
+        return self._narrow[0], self._narrow[1], _cabi.I32
+
+    # -- transposed structure ----------------------------------------------------------------
+    def transpose(self):
+        """(t_indptr, t_indices, t_perm, itype) of the pattern, in the plan's index width."""
+        if self._t is None:
+            idx, ptr, itype = self.csr()
+            self._t = transpose_structure(self.rows, self.cols, idx, ptr, itype, itype) + (itype,)
+        return self._t
+
+
+def transpose_structure(rows, cols, indices, indptr, itype_in, itype_out):
+    """Run nb200_csr_transpose_structure; returns (t_indptr, t_indices, t_perm)."""
+    nnz = int(indices.numel())
+    dev = indices.device
+    odt = torch.int32 if itype_out == _cabi.I32 else torch.int64
+    with torch.cuda.device(dev):
+        t_indptr = torch.empty(cols + 1, dtype=odt, device=dev)
+        t_indices = torch.empty(nnz, dtype=odt, device=dev)
+        t_perm = torch.empty(nnz, dtype=odt, device=dev)
+        wbytes = _cabi.lib().nb200_csr_transpose_workspace_bytes(rows, cols, nnz)
+        work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+        _cabi.call("nb200_csr_transpose_structure", rows, cols, nnz, _ptr(indices), _ptr(indptr), itype_in,
+                   _ptr(t_indptr), _ptr(t_indices), _ptr(t_perm), itype_out, _ptr(work), wbytes, _stream())
+    return t_indptr, t_indices, t_perm
+
+
+def get_plan(rows, cols, indices, indptr):
+    key = (indices.data_ptr(), indptr.data_ptr(), int(indices.numel()), int(rows), int(cols), indices.device.index)
+    plan = _CACHE.get(key)
+    if plan is not None and plan.version == (indices._version, indptr._version):
+        _CACHE.move_to_end(key)
+        return plan
+    plan = PatternPlan(rows, cols, indices, indptr)
+    _CACHE[key] = plan
+    while len(_CACHE) > _CACHE_SIZE:
+        _CACHE.popitem(last=False)
+    return plan
+
+
+def clear_plan_cache():
+    _CACHE.clear()

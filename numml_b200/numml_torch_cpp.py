@@ -1,0 +1,135 @@
+"""Operator functions with the names, argument order and return shapes of the reference's
+``numml_torch_cpp`` extension module (reference ``cpp/sparse_csr.cpp:307-319``; prototypes
+``cpp/sparse_csr.hpp:32-105``), implemented on top of the C ABI in ``include/numml_b200.h``.
+
+This layer does what the reference's dispatch stubs and ATen glue do: argument checks, output
+and workspace allocation through torch's caching allocator, current-stream lookup, and turning a
+non-zero status into a ``RuntimeError``.  All tensors must be CUDA tensors on one device: there
+is no CPU implementation behind these functions.
+"""
+import ctypes
+
+import torch
+
+from . import _cabi, _plan
+
+# How grad_x = A^T g is formed in spgemv_backward: "transpose" (gather over the cached transposed
+# structure: atomic-free, deterministic, bit-identical to the reference CPU loop) or "atomic"
+# (one fused pass over A with floating-point atomics).
+spmv_backward_mode = "transpose"
+
+
+def _dtype_code(t):
+    if t.dtype == torch.float32:
+        return _cabi.F32
+    if t.dtype == torch.float64:
+        return _cabi.F64
+    raise RuntimeError(f"numml_b200 kernels support float32 and float64, got {t.dtype}")
+
+
+def _require_cuda(*tensors):
+    dev = None
+    for t in tensors:
+        if not isinstance(t, torch.Tensor):
+            raise RuntimeError(f"expected a torch.Tensor, got {type(t)}")
+        if not t.is_cuda:
+            raise RuntimeError("numml_b200 operators run on CUDA tensors only (there is no CPU path); "
+                               "move the operands to a CUDA device")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"all operands must be on the same device, got {dev} and {t.device}")
+    return dev
+
+
+def _index_tensor(t):
+    if t.dtype != torch.int64:
+        raise RuntimeError(f"CSR index arrays must be int64 (as the reference stores them), got {t.dtype}")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _values(t, like=None):
+    if like is not None and t.dtype != like.dtype:
+        raise RuntimeError(f"operands must share one floating type, got {like.dtype} and {t.dtype}")
+    t = t if t.is_contiguous() else t.contiguous()
+    if t.data_ptr() % 16 != 0:
+        t = t.clone()  # a view at an odd offset: the kernels need 16-byte aligned arrays
+    return t
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr() if t is not None and t.numel() > 0 else 0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+# -------------------------------------------------------------------------------------------------
+# SpMV                                               reference cpp/sparse_csr.hpp:32-42
+# -------------------------------------------------------------------------------------------------
+def spgemv_forward(A_rows, A_cols, A_data, A_col_ind, A_rowptr, x):
+    dev = _require_cuda(A_data, A_col_ind, A_rowptr, x)
+    A_data = _values(A_data)
+    x = _values(x, A_data)
+    plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_col_ind), _index_tensor(A_rowptr))
+    idx, ptr, itype = plan.csr()
+    with torch.cuda.device(dev):
+        y = torch.empty(A_rows, dtype=A_data.dtype, device=dev)
+        _cabi.call("nb200_spgemv_forward", A_rows, A_cols, plan.nnz, _ptr(A_data), _ptr(idx), _ptr(ptr),
+                   None, _ptr(x), _ptr(y), _dtype_code(A_data), itype, _stream())
+    return y
+
+
+def spgemv_backward(grad_z, A_rows, A_cols, A_data, A_col_ind, A_rowptr, x):
+    dev = _require_cuda(grad_z, A_data, A_col_ind, A_rowptr, x)
+    A_data = _values(A_data)
+    x = _values(x, A_data)
+    g = _values(grad_z, A_data)
+    plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_col_ind), _index_tensor(A_rowptr))
+    idx, ptr, itype = plan.csr()
+    if spmv_backward_mode == "transpose":
+        t_indptr, t_indices, t_perm, _ = plan.transpose()
+    elif spmv_backward_mode == "atomic":
+        t_indptr = t_indices = t_perm = None
+    else:
+        raise RuntimeError(f"unknown spmv_backward_mode {spmv_backward_mode!r}")
+    with torch.cuda.device(dev):
+        grad_A = torch.empty_like(A_data)
+        grad_x = torch.empty(A_cols, dtype=A_data.dtype, device=dev)
+        _cabi.call("nb200_spgemv_backward", A_rows, A_cols, plan.nnz, _ptr(A_data), _ptr(idx), _ptr(ptr),
+                   _ptr(x), _ptr(g),
+                   _ptr(t_indptr) if t_indptr is not None else None,
+                   _ptr(t_indices) if t_indptr is not None else None,
+                   _ptr(t_perm) if t_indptr is not None else None,
+                   _ptr(grad_A), _ptr(grad_x), _dtype_code(A_data), itype, _stream())
+    return [grad_A, grad_x]
+
+
+# -------------------------------------------------------------------------------------------------
+# Transpose                                          reference cpp/sparse_csr.hpp:57-64
+# -------------------------------------------------------------------------------------------------
+def csr_transpose_forward(A_rows, A_columns, A_data, A_indices, A_indptr):
+    dev = _require_cuda(A_data, A_indices, A_indptr)
+    A_data = _values(A_data)
+    A_indices, A_indptr = _index_tensor(A_indices), _index_tensor(A_indptr)
+    nnz = int(A_indices.numel())
+    # the returned arrays are int64 like the reference's, produced directly at that width
+    t_indptr, t_indices, t_perm = _plan.transpose_structure(A_rows, A_columns, A_indices, A_indptr,
+                                                            _cabi.I64, _cabi.I64)
+    with torch.cuda.device(dev):
+        At_data = torch.empty_like(A_data)
+        _cabi.call("nb200_gather", nnz, _ptr(A_data), _ptr(t_perm), _ptr(At_data),
+                   _dtype_code(A_data), _cabi.I64, _stream())
+    return [At_data, t_indices, t_indptr, t_perm]
+
+
+def csr_transpose_backward(grad_At, At_to_A_idx):
+    dev = _require_cuda(grad_At, At_to_A_idx)
+    grad_At = _values(grad_At)
+    idx = _index_tensor(At_to_A_idx)
+    with torch.cuda.device(dev):
+        grad_A = torch.empty_like(grad_At)
+        _cabi.call("nb200_scatter", int(grad_At.numel()), _ptr(grad_At), _ptr(idx), _ptr(grad_A),
+                   _dtype_code(grad_At), _cabi.I64, _stream())
+    return grad_A

@@ -1,0 +1,148 @@
+"""GPU parity of SpMV forward/backward and the CSR transpose, called through the operator
+functions that sit directly on the C ABI.  Checked against the committed golden vectors (made by
+the reference itself) and against the CPU oracle on seeded inputs."""
+import pytest
+import torch
+
+from parity import assert_close, assert_same, case, case_names
+from numml_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from numml_b200 import numml_torch_cpp
+    return numml_torch_cpp
+
+
+def dev(*ts):
+    return [t.cuda() for t in ts]
+
+
+@pytest.mark.parametrize("mode", ["transpose", "atomic"])
+def test_golden_spmv(golden_ops, ops, mode):
+    ops.spmv_backward_mode = mode
+    try:
+        for name in case_names(golden_ops, "spmv_"):
+            c = case(golden_ops, name)
+            m, n = int(c["shape"][0]), int(c["shape"][1])
+            d, i, p, x, g = dev(c["data"], c["indices"], c["indptr"], c["x"], c["g"])
+            y = ops.spgemv_forward(m, n, d, i, p, x)
+            gA, gx = ops.spgemv_backward(g, m, n, d, i, p, x)
+            if "longrows" in name:       # warp-per-row kernel: different summation order
+                assert_close(c["y"], y, name)
+            else:                        # row-streaming kernel keeps the reference's order
+                assert_same(c["y"], y, name)
+            assert_same(c["grad_A"], gA, name)
+            if mode == "transpose" and "longrows" not in name:
+                assert_same(c["grad_x"], gx, name)
+            else:
+                assert_close(c["grad_x"], gx, name)
+    finally:
+        ops.spmv_backward_mode = "transpose"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("mode", ["transpose", "atomic"])
+@pytest.mark.parametrize("shape,density", [((1, 1), 1.0), ((5, 3), 0.5), ((1000, 777), 0.01), ((3000, 3000), 0.002),
+                                           ((257, 4100), 0.2), ((4099, 300), 0.01)])
+def test_random_vs_oracle(oracle, ops, dtype, mode, shape, density):
+    ops.spmv_backward_mode = mode
+    try:
+        d, i, p, (m, n) = W.random_csr(shape[0], shape[1], density, seed=7, dtype=dtype)
+        x, g = W.randn(n, 0, dtype), W.randn(m, 1, dtype)
+        y_ref = oracle.spgemv_forward(m, n, d, i, p, x)
+        gA_ref, gx_ref = oracle.spgemv_backward(g, m, n, d, i, p, x)
+        dd, di, dp, dx, dg = dev(d, i, p, x, g)
+        y = ops.spgemv_forward(m, n, dd, di, dp, dx)
+        gA, gx = ops.spgemv_backward(dg, m, n, dd, di, dp, dx)
+        assert_close(y_ref, y, "y")
+        assert_same(gA_ref, gA, "grad_A")
+        assert_close(gx_ref, gx, "grad_x")
+    finally:
+        ops.spmv_backward_mode = "transpose"
+
+
+def test_empty_matrix_and_empty_rows(ops):
+    z = torch.zeros(0, dtype=torch.float64).cuda()
+    zi = torch.zeros(0, dtype=torch.int64).cuda()
+    p = torch.zeros(6, dtype=torch.int64).cuda()
+    x = torch.ones(4, dtype=torch.float64).cuda()
+    y = ops.spgemv_forward(5, 4, z, zi, p, x)
+    assert y.shape == (5,) and torch.all(y == 0)
+    gA, gx = ops.spgemv_backward(torch.ones(5, dtype=torch.float64).cuda(), 5, 4, z, zi, p, x)
+    assert gA.numel() == 0 and torch.all(gx == 0)
+
+
+@pytest.mark.parametrize("n,dtype", [(64, torch.float32), (40, torch.float64)])
+def test_stencils_bit_exact(oracle, ops, n, dtype):
+    """Stencil matrices go through the row-streaming kernels, whose sums are taken in the
+    reference's order: everything must be bit-identical to the CPU oracle."""
+    gen = W.poisson2d_5pt if dtype == torch.float32 else W.poisson3d_7pt
+    d, i, p, (m, k) = gen(n, dtype)
+    x, g = W.randn(k, 0, dtype), W.randn(m, 1, dtype)
+    dd, di, dp, dx, dg = dev(d, i, p, x, g)
+    assert_same(oracle.spgemv_forward(m, k, d, i, p, x), ops.spgemv_forward(m, k, dd, di, dp, dx), "y")
+    gA_ref, gx_ref = oracle.spgemv_backward(g, m, k, d, i, p, x)
+    gA, gx = ops.spgemv_backward(dg, m, k, dd, di, dp, dx)
+    assert_same(gA_ref, gA, "grad_A")
+    assert_same(gx_ref, gx, "grad_x")
+
+
+def test_int64_index_path(oracle, ops):
+    """The kernels also read the int64 arrays exactly as the reference stores them."""
+    from numml_b200 import _plan
+    _plan.force_int64 = True
+    _plan.clear_plan_cache()
+    try:
+        d, i, p, (m, n) = W.poisson3d_7pt(24, torch.float64)
+        x, g = W.randn(n, 0, torch.float64), W.randn(m, 1, torch.float64)
+        dd, di, dp, dx, dg = dev(d, i, p, x, g)
+        assert_same(oracle.spgemv_forward(m, n, d, i, p, x), ops.spgemv_forward(m, n, dd, di, dp, dx), "y")
+        gA_ref, gx_ref = oracle.spgemv_backward(g, m, n, d, i, p, x)
+        gA, gx = ops.spgemv_backward(dg, m, n, dd, di, dp, dx)
+        assert_same(gA_ref, gA, "grad_A")
+        assert_same(gx_ref, gx, "grad_x")
+    finally:
+        _plan.force_int64 = False
+        _plan.clear_plan_cache()
+
+
+def test_golden_transpose(golden_ops, ops):
+    for name in case_names(golden_ops, "transpose_"):
+        c = case(golden_ops, name)
+        m, n = int(c["shape"][0]), int(c["shape"][1])
+        d, i, p = dev(c["data"], c["indices"], c["indptr"])
+        td, ti, tp, perm = ops.csr_transpose_forward(m, n, d, i, p)
+        for k, v in (("t_data", td), ("t_indices", ti), ("t_indptr", tp), ("t_perm", perm)):
+            assert_same(c[k], v, f"{name}/{k}")
+        assert_same(c["grad_A"], ops.csr_transpose_backward(c["grad_At"].cuda(), perm), name)
+
+
+@pytest.mark.parametrize("shape,density", [((512, 64), 0.5), ((64, 512), 0.5), ((20000, 30000), 0.0005),
+                                           ((3, 100000), 0.3), ((70000, 2), 0.5), ((1, 1), 1.0)])
+def test_transpose_vs_oracle(oracle, ops, shape, density):
+    d, i, p, (m, n) = W.random_csr(shape[0], shape[1], density, seed=3, dtype=torch.float64)
+    ref = oracle.csr_transpose_forward(m, n, d, i, p)
+    got = ops.csr_transpose_forward(m, n, *dev(d, i, p))
+    for a, b, what in zip(ref, got, ("t_data", "t_indices", "t_indptr", "t_perm")):
+        assert_same(a, b, what)
+
+
+def test_transpose_full_size_property(ops):
+    """At a benchmark-scale size: transposing twice gives the matrix back, and the permutation
+    is a bijection (size-independent properties, no oracle needed)."""
+    d, i, p, (m, n) = W.poisson3d_7pt(96, torch.float64)
+    d = W.randn(d.numel(), 5, torch.float64)
+    dd, di, dp = dev(d, i, p)
+    td, ti, tp, perm = ops.csr_transpose_forward(m, n, dd, di, dp)
+    assert torch.equal(torch.sort(perm).values, torch.arange(d.numel(), device="cuda"))
+    d2, i2, p2, _ = ops.csr_transpose_forward(n, m, td, ti, tp)
+    assert torch.equal(d2, dd) and torch.equal(i2, di) and torch.equal(p2, dp)
+
+
+def test_cpu_tensors_are_rejected(ops):
+    d, i, p, (m, n) = W.poisson2d_5pt(4, torch.float32)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.spgemv_forward(m, n, d, i, p, torch.ones(n))
