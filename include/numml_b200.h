@@ -116,6 +116,31 @@ NB200_API int nb200_scatter(int64_t n, const void* src, const void* idx, void* d
 NB200_API int nb200_narrow_indices(int64_t n, const int64_t* in64, int32_t* out32, nb200_stream stream);
 NB200_API int nb200_widen_indices(int64_t n, const int32_t* in32, int64_t* out64, nb200_stream stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * SpMM forward  C = A B, B dense row-major [cols, K], C dense row-major [rows, K].
+ * Replaces spdmm_forward (reference cpp/sparse_csr.hpp:81-85, CPU cpp/sparse_csr_cpu.cpp:562-602,
+ * CUDA cpp/sparse_csr_cuda.cu:547-603).  Each output element is summed over the row's entries in
+ * storage order with unfused multiply and add: bit-identical to the reference CPU loop.
+ * `perm` (itype, may be NULL) as in nb200_spgemv_forward: with a transposed structure this call
+ * computes grad_B = A^T grad_C of spdmm_backward without atomics.  128-bit loads are used when
+ * K * sizeof(value) is a multiple of 16 and B, C are 16-byte aligned.
+ * ------------------------------------------------------------------------------------------- */
+NB200_API int nb200_spdmm_forward(int64_t rows, int64_t cols, int64_t K, int64_t nnz,
+                                  const void* data, const void* indices, const void* indptr,
+                                  const void* perm, const void* B, void* C,
+                                  int dtype, int itype, nb200_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * SpMM backward, masked part: grad_A[k] = <grad_C[row(k), :], B[col(k), :]>.
+ * Replaces the grad_A half of spdmm_backward (reference cpp/sparse_csr.hpp:87-91, CPU
+ * cpp/sparse_csr_cpu.cpp:624-636, CUDA cpp/sparse_csr_cuda.cu:611-645); the grad_B half is
+ * nb200_spdmm_forward on the transposed structure.
+ * ------------------------------------------------------------------------------------------- */
+NB200_API int nb200_spdmm_backward_grad_A(int64_t rows, int64_t cols, int64_t K, int64_t nnz,
+                                          const void* indices, const void* indptr,
+                                          const void* B, const void* grad_C, void* grad_A,
+                                          int dtype, int itype, nb200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

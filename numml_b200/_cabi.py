@@ -26,6 +26,8 @@ SIGNATURES = {
     "nb200_scatter": (_int, [_i64, _vp, _vp, _vp, _int, _int, _vp]),
     "nb200_narrow_indices": (_int, [_i64, _vp, _vp, _vp]),
     "nb200_widen_indices": (_int, [_i64, _vp, _vp, _vp]),
+    "nb200_spdmm_forward": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
+    "nb200_spdmm_backward_grad_A": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
 }
 
 _lib = None

@@ -1,0 +1,259 @@
+// Sparse x dense products (C = A B with dense row-major B) and the masked gradient
+// grad_A[k] = <grad_C[row(k),:], B[col(k),:]> for CSR on sm_100a.
+//
+// A group of G lanes (G = 8, 16 or 32, chosen from the number of dense columns) owns one row of
+// A.  The group reads the row's (column, value) pairs G at a time with one coalesced load and
+// broadcasts them with shuffles; every lane owns VEC consecutive dense columns (one 128-bit
+// load per referenced row of B) and keeps its slice of the output row in registers.  The sum
+// over the row's entries is taken in storage order with separate multiply and add, so each
+// output element is bit-identical to a sequential CPU loop.  With `perm` the values are read as
+// data[perm[k]]: the same kernel then computes grad_B = A^T grad_C over a cached transposed
+// structure without atomics.
+#include "common.cuh"
+
+namespace nb200 {
+
+template <typename T, int VEC> struct Vec;
+template <> struct Vec<float, 4> { using type = float4; };
+template <> struct Vec<double, 2> { using type = double2; };
+template <> struct Vec<float, 1> { using type = float; };
+template <> struct Vec<double, 1> { using type = double; };
+
+template <typename T, int VEC>
+__device__ __forceinline__ void load_vec(const T* p, T (&v)[VEC]) {
+    using V = typename Vec<T, VEC>::type;
+    const V t = __ldg(reinterpret_cast<const V*>(p));
+    const T* s = reinterpret_cast<const T*>(&t);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) v[j] = s[j];
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ void store_vec(T* p, const T (&v)[VEC]) {
+    using V = typename Vec<T, VEC>::type;
+    V t;
+    T* s = reinterpret_cast<T*>(&t);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) s[j] = v[j];
+    *reinterpret_cast<V*>(p) = t;
+}
+
+// ---------------------------------------------------------------------------------------------
+// C[r, :] = sum_k A[r, k] B[k, :]
+// ---------------------------------------------------------------------------------------------
+template <typename T, typename I, int VEC, int G, bool PERM>
+__global__ void __launch_bounds__(256)
+spdmm_forward_kernel(int64_t rows, int64_t K, const T* __restrict__ data, const I* __restrict__ indices,
+                     const I* __restrict__ indptr, const I* __restrict__ perm,
+                     const T* __restrict__ B, T* __restrict__ C) {
+    constexpr int ROWS_PER_WARP = 32 / G;
+    const int lane = threadIdx.x & 31;
+    const int gl = lane % G;                 // lane within the group
+    const int gbase = lane - gl;             // first lane of the group (shuffle source offset)
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t r = warp * ROWS_PER_WARP + lane / G;
+    const bool active = r < rows;
+    const int64_t s = active ? (int64_t)indptr[r] : 0;
+    const int64_t e = active ? (int64_t)indptr[r + 1] : 0;
+
+    for (int64_t cb = 0; cb < K; cb += (int64_t)G * VEC) {   // one pass per tile of G*VEC dense columns
+        const int64_t col = cb + (int64_t)gl * VEC;
+        const bool col_ok = col < K;
+        T acc[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[j] = 0;
+        // all groups of the warp iterate together so that the shuffles stay convergent
+        int64_t len = e - s;
+#pragma unroll
+        for (int o = G; o < 32; o <<= 1) len = max(len, __shfl_xor_sync(0xffffffffu, len, o));
+        for (int64_t off = 0; off < len; off += G) {
+            const int64_t k = s + off + gl;
+            I c_mine = 0;
+            T v_mine = 0;
+            if (k < e) {
+                c_mine = indices[k];
+                v_mine = PERM ? ldg(data + perm[k]) : data[k];
+            }
+            const int cnt = (int)min((int64_t)G, e - s - off);   // <= 0 for groups that are done
+#pragma unroll 4
+            for (int j = 0; j < G; ++j) {
+                const I c = __shfl_sync(0xffffffffu, c_mine, gbase + j);
+                const T v = __shfl_sync(0xffffffffu, v_mine, gbase + j);
+                if (j < cnt && col_ok) {
+                    T b[VEC];
+                    load_vec<T, VEC>(B + (int64_t)c * K + col, b);
+#pragma unroll
+                    for (int q = 0; q < VEC; ++q) acc[q] = add_rn(acc[q], mul_rn(v, b[q]));
+                }
+            }
+        }
+        if (active && col_ok) store_vec<T, VEC>(C + r * K + col, acc);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// grad_A[k] = sum_c grad_C[row(k), c] * B[col(k), c]
+// ---------------------------------------------------------------------------------------------
+template <typename T, typename I, int VEC, int G>
+__global__ void __launch_bounds__(256)
+spdmm_grad_A_kernel(int64_t rows, int64_t K, const I* __restrict__ indices, const I* __restrict__ indptr,
+                    const T* __restrict__ B, const T* __restrict__ grad_C, T* __restrict__ grad_A) {
+    constexpr int ROWS_PER_WARP = 32 / G;
+    const int lane = threadIdx.x & 31;
+    const int gl = lane % G;
+    const int gbase = lane - gl;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t r = warp * ROWS_PER_WARP + lane / G;
+    const bool active = r < rows;
+    const int64_t s = active ? (int64_t)indptr[r] : 0;
+    const int64_t e = active ? (int64_t)indptr[r + 1] : 0;
+    const bool single_tile = K <= (int64_t)G * VEC;
+
+    T g0[VEC];                                  // this lane's slice of grad_C[r, :] (first tile)
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) g0[j] = 0;
+    if (active && (int64_t)gl * VEC < K) load_vec<T, VEC>(grad_C + r * K + (int64_t)gl * VEC, g0);
+
+    int64_t len = e - s;
+#pragma unroll
+    for (int o = G; o < 32; o <<= 1) len = max(len, __shfl_xor_sync(0xffffffffu, len, o));
+    for (int64_t off = 0; off < len; off += G) {
+        const int64_t k = s + off + gl;
+        const I c_mine = (k < e) ? indices[k] : (I)0;
+        const int cnt = (int)min((int64_t)G, e - s - off);
+        T out_mine = 0;
+#pragma unroll 2
+        for (int j = 0; j < G; ++j) {
+            const I c = __shfl_sync(0xffffffffu, c_mine, gbase + j);
+            T part = 0;
+            if (j < cnt) {
+                const T* brow = B + (int64_t)c * K;
+                if ((int64_t)gl * VEC < K) {
+                    T b[VEC];
+                    load_vec<T, VEC>(brow + (int64_t)gl * VEC, b);
+#pragma unroll
+                    for (int q = 0; q < VEC; ++q) part += g0[q] * b[q];
+                }
+                if (!single_tile) {
+                    for (int64_t col = (int64_t)(G + gl) * VEC; col < K; col += (int64_t)G * VEC) {
+                        T b[VEC], g[VEC];
+                        load_vec<T, VEC>(brow + col, b);
+                        load_vec<T, VEC>(grad_C + r * K + col, g);
+#pragma unroll
+                        for (int q = 0; q < VEC; ++q) part += g[q] * b[q];
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = G / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (gl == j) out_mine = part;
+        }
+        if (k < e) grad_A[k] = out_mine;
+    }
+}
+
+template <typename T, typename I, int VEC, int G>
+int spdmm_forward_cfg(int64_t rows, int64_t K, const T* data, const I* indices, const I* indptr, const I* perm,
+                      const T* B, T* C, cudaStream_t st) {
+    const int64_t warps = ceil_div(rows, (int64_t)(32 / G));
+    const int64_t grid = ceil_div(warps, (int64_t)8);
+    if (grid > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
+    if (perm)
+        spdmm_forward_kernel<T, I, VEC, G, true><<<(unsigned)grid, 256, 0, st>>>(rows, K, data, indices, indptr, perm, B, C);
+    else
+        spdmm_forward_kernel<T, I, VEC, G, false><<<(unsigned)grid, 256, 0, st>>>(rows, K, data, indices, indptr, perm, B, C);
+    return launch_status();
+}
+
+template <typename T, typename I, int VEC, int G>
+int spdmm_grad_A_cfg(int64_t rows, int64_t K, const I* indices, const I* indptr, const T* B, const T* grad_C,
+                     T* grad_A, cudaStream_t st) {
+    const int64_t warps = ceil_div(rows, (int64_t)(32 / G));
+    const int64_t grid = ceil_div(warps, (int64_t)8);
+    if (grid > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
+    spdmm_grad_A_kernel<T, I, VEC, G><<<(unsigned)grid, 256, 0, st>>>(rows, K, indices, indptr, B, grad_C, grad_A);
+    return launch_status();
+}
+
+// Lanes per row: the smallest of 8 / 16 / 32 that covers the K dense columns in one tile.
+template <int VEC>
+static inline int pick_group(int64_t K) {
+    if (K <= 8 * VEC) return 8;
+    if (K <= 16 * VEC) return 16;
+    return 32;
+}
+
+template <typename T, typename I>
+int spdmm_forward_launch(int64_t rows, int64_t K, const T* data, const I* indices, const I* indptr, const I* perm,
+                         const T* B, T* C, cudaStream_t st) {
+    if (rows == 0 || K == 0) return NB200_OK;
+    constexpr int V = 16 / sizeof(T);
+    const bool vec_ok = (K % V == 0) && aligned16(B) && aligned16(C);
+#define NB200_FWD(VEC_, G_) spdmm_forward_cfg<T, I, VEC_, G_>(rows, K, data, indices, indptr, perm, B, C, st)
+    if (vec_ok) {
+        switch (pick_group<V>(K)) {
+            case 8: return NB200_FWD(V, 8);
+            case 16: return NB200_FWD(V, 16);
+            default: return NB200_FWD(V, 32);
+        }
+    }
+    switch (pick_group<1>(K)) {
+        case 8: return NB200_FWD(1, 8);
+        case 16: return NB200_FWD(1, 16);
+        default: return NB200_FWD(1, 32);
+    }
+#undef NB200_FWD
+}
+
+template <typename T, typename I>
+int spdmm_grad_A_launch(int64_t rows, int64_t K, const I* indices, const I* indptr, const T* B, const T* grad_C,
+                        T* grad_A, cudaStream_t st) {
+    if (rows == 0) return NB200_OK;
+    constexpr int V = 16 / sizeof(T);
+    const bool vec_ok = (K % V == 0) && aligned16(B) && aligned16(grad_C) && K > 0;
+#define NB200_GA(VEC_, G_) spdmm_grad_A_cfg<T, I, VEC_, G_>(rows, K, indices, indptr, B, grad_C, grad_A, st)
+    if (vec_ok) {
+        switch (pick_group<V>(K)) {
+            case 8: return NB200_GA(V, 8);
+            case 16: return NB200_GA(V, 16);
+            default: return NB200_GA(V, 32);
+        }
+    }
+    switch (pick_group<1>(K)) {
+        case 8: return NB200_GA(1, 8);
+        case 16: return NB200_GA(1, 16);
+        default: return NB200_GA(1, 32);
+    }
+#undef NB200_GA
+}
+
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" int nb200_spdmm_forward(int64_t rows, int64_t cols, int64_t K, int64_t nnz,
+                                   const void* data, const void* indices, const void* indptr, const void* perm,
+                                   const void* B, void* C, int dtype, int itype, nb200_stream stream) {
+    (void)cols;
+    if (rows < 0 || cols < 0 || K < 0 || nnz < 0) return NB200_ERR_BAD_ARG;
+    if (rows == 0 || K == 0) return NB200_OK;
+    if (!indptr || !C || (nnz > 0 && (!data || !indices || !B))) return NB200_ERR_BAD_ARG;
+    if (itype == NB200_I32 && nnz > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
+    return NB200_DISPATCH(dtype, itype,
+        (spdmm_forward_launch<T, I>(rows, K, (const T*)data, (const I*)indices, (const I*)indptr, (const I*)perm,
+                                    (const T*)B, (T*)C, as_stream(stream))));
+}
+
+extern "C" int nb200_spdmm_backward_grad_A(int64_t rows, int64_t cols, int64_t K, int64_t nnz,
+                                           const void* indices, const void* indptr,
+                                           const void* B, const void* grad_C, void* grad_A,
+                                           int dtype, int itype, nb200_stream stream) {
+    (void)cols;
+    if (rows < 0 || cols < 0 || K < 0 || nnz < 0) return NB200_ERR_BAD_ARG;
+    if (rows == 0 || nnz == 0) return NB200_OK;
+    if (!indptr || !indices || !grad_A || (K > 0 && (!B || !grad_C))) return NB200_ERR_BAD_ARG;
+    if (itype == NB200_I32 && nnz > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
+    return NB200_DISPATCH(dtype, itype,
+        (spdmm_grad_A_launch<T, I>(rows, K, (const I*)indices, (const I*)indptr, (const T*)B, (const T*)grad_C,
+                                   (T*)grad_A, as_stream(stream))));
+}

@@ -133,3 +133,49 @@ def csr_transpose_backward(grad_At, At_to_A_idx):
         _cabi.call("nb200_scatter", int(grad_At.numel()), _ptr(grad_At), _ptr(idx), _ptr(grad_A),
                    _dtype_code(grad_At), _cabi.I64, _stream())
     return grad_A
+
+
+# -------------------------------------------------------------------------------------------------
+# SpMM                                               reference cpp/sparse_csr.hpp:81-91
+# -------------------------------------------------------------------------------------------------
+def _dense(t, like):
+    if t.ndim != 2:
+        raise RuntimeError(f"expected a 2-D dense matrix, got {t.ndim} dimensions")
+    return _values(t, like)
+
+
+def spdmm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B):
+    dev = _require_cuda(A_data, A_indices, A_indptr, B)
+    A_data = _values(A_data)
+    B = _dense(B, A_data)
+    if B.shape[0] != A_cols:
+        raise RuntimeError(f"dense operand has {B.shape[0]} rows, expected {A_cols}")
+    plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
+    idx, ptr, itype = plan.csr()
+    K = int(B.shape[1])
+    with torch.cuda.device(dev):
+        C = torch.empty((A_rows, K), dtype=A_data.dtype, device=dev)
+        _cabi.call("nb200_spdmm_forward", A_rows, A_cols, K, plan.nnz, _ptr(A_data), _ptr(idx), _ptr(ptr), None,
+                   _ptr(B), _ptr(C), _dtype_code(A_data), itype, _stream())
+    return C
+
+
+def spdmm_backward(A_rows, A_cols, A_data, A_indices, A_indptr, B, grad_C):
+    dev = _require_cuda(A_data, A_indices, A_indptr, B, grad_C)
+    A_data = _values(A_data)
+    B = _dense(B, A_data)
+    G = _dense(grad_C, A_data)
+    plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
+    idx, ptr, itype = plan.csr()
+    t_indptr, t_indices, t_perm, _ = plan.transpose()
+    K = int(B.shape[1])
+    code = _dtype_code(A_data)
+    with torch.cuda.device(dev):
+        grad_A = torch.empty_like(A_data)
+        grad_B = torch.empty((A_cols, K), dtype=A_data.dtype, device=dev)
+        _cabi.call("nb200_spdmm_backward_grad_A", A_rows, A_cols, K, plan.nnz, _ptr(idx), _ptr(ptr),
+                   _ptr(B), _ptr(G), _ptr(grad_A), code, itype, _stream())
+        # grad_B = A^T grad_C: the forward kernel over the transposed structure, values via the permutation
+        _cabi.call("nb200_spdmm_forward", A_cols, A_rows, K, plan.nnz, _ptr(A_data), _ptr(t_indices), _ptr(t_indptr),
+                   _ptr(t_perm), _ptr(G), _ptr(grad_B), code, itype, _stream())
+    return [grad_A, grad_B]
