@@ -141,6 +141,64 @@ NB200_API int nb200_spdmm_backward_grad_A(int64_t rows, int64_t cols, int64_t K,
                                           const void* B, const void* grad_C, void* grad_A,
                                           int dtype, int itype, nb200_stream stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * SpGEMM  C = A B, hash-based, in two phases.      Replaces spgemm_forward (reference
+ * cpp/sparse_csr.hpp:45-48, CPU cpp/sparse_csr_cpu.cpp:117-216, CUDA
+ * cpp/sparse_csr_gemm_cuda.cu:223-302).
+ *
+ *   1. nb200_spgemm_plan      counts the products of every row of A, bins the rows and writes a
+ *                             header of 16 int64 words at the start of `workspace`:
+ *                             [0..3] rows per bin, [4] spill slots needed by the symbolic phase,
+ *                             [5] largest product count of a row.
+ *   2. nb200_spgemm_symbolic  counts the distinct columns of every row of C with per-bin hash
+ *                             tables (shared memory; rows with more than 4096 products use
+ *                             `spill`, an array of `spill_slots` uint32), writes C_indptr
+ *                             (int64, A_rows+1 entries) and extends the header: [8..11] rows per
+ *                             bin for the numeric phase, [12] its spill slots, [13] nnz(C),
+ *                             [14] non-zero if a spill area was too small.
+ *   3. nb200_spgemm_numeric   fills C_indices (int64, ascending within a row) and C_data;
+ *                             `spill` must hold spill_slots * (sizeof(value) + 4) bytes.
+ *
+ * The caller reads the header (a device-to-host copy of 128 bytes) after steps 1 and 2 to size
+ * the spill areas and the outputs.  C's pattern is purely structural: numerically cancelled
+ * entries are stored as zeros, like the reference's.  C_indptr / C_indices are bit-identical to
+ * the reference's; values are accumulated with atomics (order not fixed).
+ * `workspace` must hold nb200_spgemm_workspace_bytes(A_rows) bytes and be kept between the calls.
+ * ------------------------------------------------------------------------------------------- */
+NB200_API size_t nb200_spgemm_workspace_bytes(int64_t A_rows);
+NB200_API int nb200_spgemm_plan(int64_t A_rows, int64_t A_cols, int64_t A_nnz,
+                                const void* A_indices, const void* A_indptr, const void* B_indptr, int itype,
+                                void* workspace, size_t workspace_bytes, nb200_stream stream);
+NB200_API int nb200_spgemm_symbolic(int64_t A_rows, int64_t A_cols, int64_t B_cols,
+                                    const void* A_indices, const void* A_indptr,
+                                    const void* B_indices, const void* B_indptr, int itype,
+                                    void* workspace, size_t workspace_bytes, void* spill, int64_t spill_slots,
+                                    int64_t* C_indptr, nb200_stream stream);
+NB200_API int nb200_spgemm_numeric(int64_t A_rows, int64_t A_cols, int64_t B_cols,
+                                   const void* A_data, const void* A_indices, const void* A_indptr,
+                                   const void* B_data, const void* B_indices, const void* B_indptr,
+                                   int dtype, int itype, void* workspace, size_t workspace_bytes,
+                                   void* spill, int64_t spill_slots,
+                                   const int64_t* C_indptr, int64_t* C_indices, void* C_data, nb200_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * SpGEMM backward.                                 Replaces spgemm_backward (reference
+ * cpp/sparse_csr.hpp:50-54, CPU cpp/sparse_csr_cpu.cpp:218-307, CUDA
+ * cpp/sparse_csr_gemm_cuda.cu:311-371,663-771).
+ *   grad_A = (grad_C B^T) restricted to the pattern of A,
+ *   grad_B = (A^T grad_C) restricted to the pattern of B,
+ * with grad_C given on C's pattern (C_indices / C_indptr int64, columns ascending).  At_* is the
+ * transposed structure of A (nb200_csr_transpose_structure, index width `itype`).  No atomics;
+ * sums are taken in the reference's order with unfused multiply and add (bit-identical).
+ * ------------------------------------------------------------------------------------------- */
+NB200_API int nb200_spgemm_backward(int64_t A_rows, int64_t A_cols, int64_t A_nnz,
+                                    const void* A_data, const void* A_indices, const void* A_indptr,
+                                    const void* At_indptr, const void* At_indices, const void* At_perm,
+                                    int64_t B_rows, int64_t B_cols, int64_t B_nnz,
+                                    const void* B_data, const void* B_indices, const void* B_indptr,
+                                    const void* grad_C, const int64_t* C_indices, const int64_t* C_indptr,
+                                    void* grad_A, void* grad_B, int dtype, int itype, nb200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

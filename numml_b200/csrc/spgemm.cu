@@ -1,0 +1,519 @@
+// Hash-based SpGEMM C = A B (symbolic row-nnz count, then numeric fill with column-sorted rows)
+// and its masked backward, for CSR on sm_100a.
+//
+// Rows of C are binned by size (upper bound = number of products for the symbolic phase, exact
+// nnz for the numeric phase).  Each bin has a team size and an open-addressing hash table:
+//     bin 0:   8 lanes per row,  64-slot table in shared memory      (size <= 32)
+//     bin 1:  32 lanes per row, 512-slot table in shared memory      (size <= 256)
+//     bin 2: 256 threads per row, 8192-slot (symbolic) / 4096-slot (numeric) table in shared memory
+//     bin 3: 256 threads per row, table in a caller-provided global-memory spill area
+// Column keys are inserted with atomicCAS and linear probing (load factor <= 1/2); the numeric
+// phase accumulates values with shared/global atomics, then sorts the whole table by key with a
+// bitonic network (empty slots sort last) and writes the first nnz entries.  The pattern is
+// purely structural: a product that cancels numerically still yields a stored zero, as in the
+// reference.
+//
+// Backward is atomic-free: grad_A[(i,j)] walks row j of B against row i of C in ascending
+// column order; grad_B[(j,c)] walks column j of A (through the cached transposed structure of
+// A) in ascending row order and looks c up in the corresponding rows of C.  Both orders are the
+// reference's, and multiply/add are unfused, so the gradients are bit-identical to its CPU loops.
+#include "primitives.cuh"
+
+namespace nb200 {
+
+constexpr uint32_t kEmptyKey = 0xffffffffu;
+constexpr int kBins = 4;
+constexpr int kHeaderWords = 16;   // int64 words at the start of the workspace
+// header layout (int64):
+//   [0..3]  rows per bin, symbolic classification (by number of products)
+//   [4]     spill slots needed by the symbolic phase (bin 3 tables)
+//   [5]     largest per-row number of products
+//   [8..11] rows per bin, numeric classification (by nnz of the output row)
+//   [12]    spill slots needed by the numeric phase
+//   [13]    nnz(C)
+//   [14]    error word (non-zero: a spill table was too small)
+
+__host__ __device__ inline int bin_of(int64_t size, bool numeric) {
+    if (size <= 32) return 0;
+    if (size <= 256) return 1;
+    if (size <= (numeric ? 2048 : 4096)) return 2;
+    return 3;
+}
+
+__device__ __forceinline__ int64_t spill_table_size(int64_t size) {
+    int64_t t = 64;
+    while (t < 2 * size) t <<= 1;
+    return t;
+}
+
+__device__ __forceinline__ uint32_t hash_key(uint32_t c) { return c * 2654435761u; }
+
+// Insert key c; returns its slot.  The table never fills (load factor <= 1/2 by construction).
+__device__ __forceinline__ uint32_t table_insert(uint32_t* keys, uint32_t mask, int shift, uint32_t c) {
+    uint32_t slot = (hash_key(c) >> shift) & mask;
+    while (true) {
+        const uint32_t old = atomicCAS(keys + slot, kEmptyKey, c);
+        if (old == kEmptyKey || old == c) return slot;
+        slot = (slot + 1) & mask;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Planning kernels
+// ---------------------------------------------------------------------------------------------
+template <typename I>
+__global__ void spgemm_products_kernel(int64_t rows, const I* __restrict__ A_indices, const I* __restrict__ A_indptr,
+                                       const I* __restrict__ B_indptr, int32_t* __restrict__ size_out,
+                                       unsigned long long* __restrict__ header) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    long long local_max = 0;
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += stride) {
+        long long ub = 0;
+        for (int64_t a = (int64_t)A_indptr[r]; a < (int64_t)A_indptr[r + 1]; ++a) {
+            const int64_t j = (int64_t)A_indices[a];
+            ub += (long long)B_indptr[j + 1] - (long long)B_indptr[j];
+        }
+        if (ub > 0x7fffffffLL) ub = 0x7fffffffLL;
+        size_out[r] = (int32_t)ub;
+        local_max = max(local_max, ub);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local_max = max(local_max, __shfl_xor_sync(0xffffffffu, local_max, o));
+    if ((threadIdx.x & 31) == 0 && local_max > 0) atomicMax(header + 5, (unsigned long long)local_max);
+}
+
+// Distribute rows into per-bin lists (warp-aggregated appends) and size the spill tables.
+__global__ void spgemm_classify_kernel(int64_t rows, const int32_t* __restrict__ size_in, bool numeric,
+                                       int32_t* __restrict__ lists, int64_t* __restrict__ spill_off,
+                                       unsigned long long* __restrict__ header) {
+    const int hb = numeric ? 8 : 0;
+    const int lane = threadIdx.x & 31;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t rows_pad = (rows + 31) & ~(int64_t)31;
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < rows_pad; r += stride) {
+        const bool ok = r < rows;
+        const int32_t size = ok ? size_in[r] : 0;
+        const int bin = ok ? bin_of(size, numeric) : kBins;
+        const uint32_t peers = __match_any_sync(0xffffffffu, bin);
+        if (ok) {
+            const int leader = __ffs(peers) - 1;
+            unsigned long long base = 0;
+            if (lane == leader) base = atomicAdd(header + hb + bin, (unsigned long long)__popc(peers));
+            base = __shfl_sync(peers, base, leader);
+            const int64_t pos = (int64_t)base + __popc(peers & ((1u << lane) - 1u));
+            lists[(int64_t)bin * rows + pos] = (int32_t)r;
+            if (bin == 3) spill_off[pos] = (int64_t)atomicAdd(header + hb + 4, (unsigned long long)spill_table_size(size));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Team helpers
+// ---------------------------------------------------------------------------------------------
+template <int TEAM>
+__device__ __forceinline__ void team_sync() {
+    if (TEAM >= 256) __syncthreads(); else __syncwarp();
+}
+
+template <int TEAM>
+__device__ __forceinline__ int team_sum(int v, int* scratch) {
+    if (TEAM <= 32) {
+#pragma unroll
+        for (int o = TEAM / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        return v;
+    } else {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+        __syncthreads();
+        int t = 0;
+        for (int w = 0; w < TEAM / 32; ++w) t += scratch[w];
+        __syncthreads();
+        return t;
+    }
+}
+
+// Bitonic sort of the whole table by key (ascending, empty slots last), values carried along.
+template <typename T, int TEAM, bool WITH_VALUES>
+__device__ __forceinline__ void team_sort(uint32_t* keys, T* vals, int64_t table, int t) {
+    for (int64_t k = 2; k <= table; k <<= 1) {
+        for (int64_t j = k >> 1; j > 0; j >>= 1) {
+            for (int64_t p = t; p < (table >> 1); p += TEAM) {
+                const int64_t i = ((p & ~(j - 1)) << 1) | (p & (j - 1));
+                const int64_t q = i | j;
+                const uint32_t a = keys[i], b = keys[q];
+                const bool up = (i & k) == 0;
+                if ((a > b) == up) {
+                    keys[i] = b; keys[q] = a;
+                    if (WITH_VALUES) { const T va = vals[i]; vals[i] = vals[q]; vals[q] = va; }
+                }
+            }
+            team_sync<TEAM>();
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Symbolic: distinct columns per row of C.  SUB lanes share one entry of A and stride over the
+// matching row of B; TEAM/SUB entries of A are in flight per team.
+// ---------------------------------------------------------------------------------------------
+template <typename I, int TEAM, int SUB, int TLOG, bool SPILL>
+__global__ void __launch_bounds__(256)
+spgemm_symbolic_kernel(const int32_t* __restrict__ list, const unsigned long long* __restrict__ count_ptr,
+                       const I* __restrict__ A_indices, const I* __restrict__ A_indptr,
+                       const I* __restrict__ B_indices, const I* __restrict__ B_indptr,
+                       const int32_t* __restrict__ size_in, const int64_t* __restrict__ spill_off,
+                       uint32_t* __restrict__ spill, int64_t spill_slots, unsigned long long* __restrict__ header,
+                       int32_t* __restrict__ row_nnz) {
+    constexpr int TEAMS = 256 / TEAM;
+    constexpr int TABLE = SPILL ? 1 : (1 << TLOG);
+    __shared__ uint32_t s_keys[TEAMS * TABLE];
+    __shared__ int s_red[8];
+    const int team = threadIdx.x / TEAM, t = threadIdx.x % TEAM;
+    const int64_t count = (int64_t)*count_ptr;
+    for (int64_t base = (int64_t)blockIdx.x * TEAMS; base < count; base += (int64_t)gridDim.x * TEAMS) {
+        const int64_t idx = base + team;
+        const bool active = idx < count;
+        const int64_t row = active ? (int64_t)list[idx] : 0;
+        uint32_t* keys = s_keys + team * TABLE;
+        int64_t table = TABLE;
+        bool usable = true;
+        if (SPILL) {
+            table = spill_table_size(size_in[row]);
+            const int64_t off = spill_off[idx];
+            usable = off + table <= spill_slots;
+            keys = spill + off;
+            if (!usable && t == 0) atomicExch(header + 14, 1ull);
+        }
+        int shift = 32;
+        for (int64_t s = table; s > 1; s >>= 1) --shift;
+        const uint32_t mask = (uint32_t)(table - 1);
+        if (usable) for (int64_t s = t; s < table; s += TEAM) keys[s] = kEmptyKey;
+        team_sync<TEAM>();
+        if (active && usable) {
+            const int64_t a_end = (int64_t)A_indptr[row + 1];
+            for (int64_t a = (int64_t)A_indptr[row] + t / SUB; a < a_end; a += TEAM / SUB) {
+                const int64_t j = (int64_t)A_indices[a];
+                const int64_t b_end = (int64_t)B_indptr[j + 1];
+                for (int64_t b = (int64_t)B_indptr[j] + t % SUB; b < b_end; b += SUB)
+                    table_insert(keys, mask, shift, (uint32_t)B_indices[b]);
+            }
+        }
+        team_sync<TEAM>();
+        int cnt = 0;
+        if (usable) for (int64_t s = t; s < table; s += TEAM) cnt += keys[s] != kEmptyKey;
+        cnt = team_sum<TEAM>(cnt, s_red);
+        if (active && t == 0) row_nnz[row] = cnt;
+        team_sync<TEAM>();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Numeric: insert (column, product) pairs, sort the table, write the row.
+// ---------------------------------------------------------------------------------------------
+template <typename T, typename I, int TEAM, int SUB, int TLOG, bool SPILL>
+__global__ void __launch_bounds__(256)
+spgemm_numeric_kernel(const int32_t* __restrict__ list, const unsigned long long* __restrict__ count_ptr,
+                      const T* __restrict__ A_data, const I* __restrict__ A_indices, const I* __restrict__ A_indptr,
+                      const T* __restrict__ B_data, const I* __restrict__ B_indices, const I* __restrict__ B_indptr,
+                      const int32_t* __restrict__ size_in, const int64_t* __restrict__ spill_off,
+                      uint32_t* __restrict__ spill_keys, T* __restrict__ spill_vals, int64_t spill_slots,
+                      unsigned long long* __restrict__ header,
+                      const int64_t* __restrict__ C_indptr, int64_t* __restrict__ C_indices, T* __restrict__ C_data) {
+    constexpr int TEAMS = 256 / TEAM;
+    constexpr int TABLE = SPILL ? 1 : (1 << TLOG);
+    __shared__ uint32_t s_keys[TEAMS * TABLE];
+    __shared__ T s_vals[TEAMS * TABLE];
+    const int team = threadIdx.x / TEAM, t = threadIdx.x % TEAM;
+    const int64_t count = (int64_t)*count_ptr;
+    for (int64_t base = (int64_t)blockIdx.x * TEAMS; base < count; base += (int64_t)gridDim.x * TEAMS) {
+        const int64_t idx = base + team;
+        const bool active = idx < count;
+        const int64_t row = active ? (int64_t)list[idx] : 0;
+        uint32_t* keys = s_keys + team * TABLE;
+        T* vals = s_vals + team * TABLE;
+        int64_t table = TABLE;
+        bool usable = true;
+        if (SPILL) {
+            table = spill_table_size(size_in[row]);
+            const int64_t off = spill_off[idx];
+            usable = off + table <= spill_slots;
+            keys = spill_keys + off;
+            vals = spill_vals + off;
+            if (!usable && t == 0) atomicExch(header + 14, 1ull);
+        }
+        int shift = 32;
+        for (int64_t s = table; s > 1; s >>= 1) --shift;
+        const uint32_t mask = (uint32_t)(table - 1);
+        if (usable) for (int64_t s = t; s < table; s += TEAM) { keys[s] = kEmptyKey; vals[s] = (T)0; }
+        team_sync<TEAM>();
+        if (active && usable) {
+            const int64_t a_end = (int64_t)A_indptr[row + 1];
+            for (int64_t a = (int64_t)A_indptr[row] + t / SUB; a < a_end; a += TEAM / SUB) {
+                const int64_t j = (int64_t)A_indices[a];
+                const T av = A_data[a];
+                const int64_t b_end = (int64_t)B_indptr[j + 1];
+                for (int64_t b = (int64_t)B_indptr[j] + t % SUB; b < b_end; b += SUB) {
+                    const uint32_t slot = table_insert(keys, mask, shift, (uint32_t)B_indices[b]);
+                    atomicAdd(vals + slot, mul_rn(av, B_data[b]));
+                }
+            }
+        }
+        team_sync<TEAM>();
+        if (usable) team_sort<T, TEAM, true>(keys, vals, table, t);
+        if (active && usable) {
+            const int64_t o0 = C_indptr[row], n = C_indptr[row + 1] - o0;
+            for (int64_t q = t; q < n; q += TEAM) {
+                C_indices[o0 + q] = (int64_t)keys[q];
+                C_data[o0 + q] = vals[q];
+            }
+        }
+        team_sync<TEAM>();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward kernels
+// ---------------------------------------------------------------------------------------------
+template <typename I>
+__device__ __forceinline__ int64_t row_of_position(const I* __restrict__ indptr, int64_t rows, int64_t k) {
+    int64_t lo = 0, hi = rows;   // largest r with indptr[r] <= k
+    while (hi - lo > 1) {
+        const int64_t mid = (lo + hi) >> 1;
+        if ((int64_t)indptr[mid] <= k) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+// grad_A[(i,j)] = sum over c in row j of B (ascending) of grad_C[(i,c)] * B[(j,c)]
+template <typename T, typename I>
+__global__ void spgemm_grad_A_kernel(int64_t A_rows, int64_t A_nnz, const I* __restrict__ A_indices,
+                                     const I* __restrict__ A_indptr, const T* __restrict__ B_data,
+                                     const I* __restrict__ B_indices, const I* __restrict__ B_indptr,
+                                     const T* __restrict__ grad_C, const int64_t* __restrict__ C_indices,
+                                     const int64_t* __restrict__ C_indptr, T* __restrict__ grad_A) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < A_nnz; k += stride) {
+        const int64_t i = row_of_position(A_indptr, A_rows, k);
+        const int64_t j = (int64_t)A_indices[k];
+        int64_t ci = C_indptr[i];
+        const int64_t ce = C_indptr[i + 1];
+        int64_t bi = (int64_t)B_indptr[j];
+        const int64_t be = (int64_t)B_indptr[j + 1];
+        T s = 0;
+        while (ci < ce && bi < be) {
+            const int64_t cc = C_indices[ci], bc = (int64_t)B_indices[bi];
+            if (cc < bc) ++ci;
+            else if (cc > bc) ++bi;
+            else { s = add_rn(s, mul_rn(grad_C[ci], B_data[bi])); ++ci; ++bi; }
+        }
+        grad_A[k] = s;
+    }
+}
+
+// grad_B[(j,c)] = sum over i in column j of A (ascending) of A[(i,j)] * grad_C[(i,c)]
+template <typename T, typename I>
+__global__ void spgemm_grad_B_kernel(int64_t B_rows, int64_t B_nnz, const I* __restrict__ B_indices,
+                                     const I* __restrict__ B_indptr, const T* __restrict__ A_data,
+                                     const I* __restrict__ At_indptr, const I* __restrict__ At_indices,
+                                     const I* __restrict__ At_perm, const T* __restrict__ grad_C,
+                                     const int64_t* __restrict__ C_indices, const int64_t* __restrict__ C_indptr,
+                                     T* __restrict__ grad_B) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < B_nnz; q += stride) {
+        const int64_t j = row_of_position(B_indptr, B_rows, q);
+        const int64_t c = (int64_t)B_indices[q];
+        T s = 0;
+        for (int64_t a = (int64_t)At_indptr[j]; a < (int64_t)At_indptr[j + 1]; ++a) {
+            const int64_t i = (int64_t)At_indices[a];
+            int64_t lo = C_indptr[i], hi = C_indptr[i + 1] - 1;
+            while (lo <= hi) {
+                const int64_t mid = (lo + hi) >> 1;
+                const int64_t cc = C_indices[mid];
+                if (cc < c) lo = mid + 1;
+                else if (cc > c) hi = mid - 1;
+                else { s = add_rn(s, mul_rn(A_data[(int64_t)At_perm[a]], grad_C[mid])); break; }
+            }
+        }
+        grad_B[q] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Workspace layout
+// ---------------------------------------------------------------------------------------------
+struct SpgemmWorkspace {
+    unsigned long long* header;
+    int32_t* size;       // products per row, later nnz per row
+    int32_t* row_nnz;
+    int32_t* lists;      // kBins x rows
+    int64_t* spill_off;  // rows
+    char* scan;
+    size_t scan_bytes;
+    bool ok;
+};
+
+static size_t spgemm_workspace_bytes(int64_t rows) {
+    const size_t r = (size_t)(rows > 0 ? rows : 1);
+    return Workspace::pad(kHeaderWords * sizeof(int64_t)) + 2 * Workspace::pad(r * sizeof(int32_t)) +
+           Workspace::pad(kBins * r * sizeof(int32_t)) + Workspace::pad(r * sizeof(int64_t)) +
+           Workspace::pad(scan_scratch_bytes(rows));
+}
+
+static SpgemmWorkspace carve(int64_t rows, void* workspace, size_t bytes) {
+    const size_t r = (size_t)(rows > 0 ? rows : 1);
+    Workspace ws(workspace, bytes);
+    SpgemmWorkspace w;
+    w.header = ws.take<unsigned long long>(kHeaderWords);
+    w.size = ws.take<int32_t>(r);
+    w.row_nnz = ws.take<int32_t>(r);
+    w.lists = ws.take<int32_t>(kBins * r);
+    w.spill_off = ws.take<int64_t>(r);
+    w.scan_bytes = scan_scratch_bytes(rows);
+    w.scan = ws.take<char>(w.scan_bytes);
+    w.ok = ws.ok();
+    return w;
+}
+
+static inline unsigned persistent_grid(int ctas_per_sm = 8) { return (unsigned)(kSMs * ctas_per_sm); }
+
+static inline unsigned flat_grid(int64_t n) {
+    const int64_t want = ceil_div(n > 0 ? n : 1, (int64_t)256);
+    return (unsigned)(want > (int64_t)kSMs * 32 ? (int64_t)kSMs * 32 : want);
+}
+
+template <typename I>
+int spgemm_plan(int64_t A_rows, const I* A_indices, const I* A_indptr, const I* B_indptr,
+                void* workspace, size_t bytes, cudaStream_t st) {
+    SpgemmWorkspace w = carve(A_rows, workspace, bytes);
+    if (!w.ok) return NB200_ERR_WORKSPACE;
+    if (cudaMemsetAsync(w.header, 0, kHeaderWords * sizeof(int64_t), st) != cudaSuccess) return NB200_ERR_CUDA;
+    if (A_rows == 0) return NB200_OK;
+    spgemm_products_kernel<I><<<flat_grid(A_rows), 256, 0, st>>>(A_rows, A_indices, A_indptr, B_indptr, w.size, w.header);
+    spgemm_classify_kernel<<<flat_grid(A_rows), 256, 0, st>>>(A_rows, w.size, false, w.lists, w.spill_off, w.header);
+    return launch_status();
+}
+
+template <typename I>
+int spgemm_symbolic(int64_t A_rows, const I* A_indices, const I* A_indptr, const I* B_indices, const I* B_indptr,
+                    void* workspace, size_t bytes, uint32_t* spill, int64_t spill_slots, int64_t* C_indptr,
+                    cudaStream_t st) {
+    SpgemmWorkspace w = carve(A_rows, workspace, bytes);
+    if (!w.ok) return NB200_ERR_WORKSPACE;
+    if (A_rows > 0) {
+        const unsigned g = persistent_grid();
+#define NB200_SYM(TEAM, SUB, TLOG, SPILL, BIN)                                                              \
+        spgemm_symbolic_kernel<I, TEAM, SUB, TLOG, SPILL><<<g, 256, 0, st>>>(                                 \
+            w.lists + (int64_t)(BIN) * A_rows, w.header + (BIN), A_indices, A_indptr, B_indices, B_indptr,  \
+            w.size, w.spill_off, spill, spill_slots, w.header, w.row_nnz)
+        NB200_SYM(8, 1, 6, false, 0);
+        NB200_SYM(32, 4, 9, false, 1);
+        NB200_SYM(256, 32, 13, false, 2);
+        NB200_SYM(256, 32, 0, true, 3);
+#undef NB200_SYM
+    }
+    int rc = exclusive_scan_i32_to_i64(A_rows, w.row_nnz, C_indptr, w.scan, w.scan_bytes, st);
+    if (rc != NB200_OK) return rc;
+    if (A_rows > 0) {
+        // numeric classification by exact row size; nnz(C) goes to header[13]
+        spgemm_classify_kernel<<<flat_grid(A_rows), 256, 0, st>>>(A_rows, w.row_nnz, true, w.lists, w.spill_off, w.header);
+    }
+    if (cudaMemcpyAsync(w.header + 13, C_indptr + A_rows, sizeof(int64_t), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+        return NB200_ERR_CUDA;
+    return launch_status();
+}
+
+template <typename T, typename I>
+int spgemm_numeric(int64_t A_rows, const T* A_data, const I* A_indices, const I* A_indptr,
+                   const T* B_data, const I* B_indices, const I* B_indptr, void* workspace, size_t bytes,
+                   void* spill, int64_t spill_slots, const int64_t* C_indptr, int64_t* C_indices, T* C_data,
+                   cudaStream_t st) {
+    SpgemmWorkspace w = carve(A_rows, workspace, bytes);
+    if (!w.ok) return NB200_ERR_WORKSPACE;
+    if (A_rows == 0) return NB200_OK;
+    // spill area: values first (8-byte aligned), keys after
+    T* spill_vals = static_cast<T*>(spill);
+    uint32_t* spill_keys = reinterpret_cast<uint32_t*>(spill_vals + (spill_slots > 0 ? spill_slots : 0));
+    const unsigned g = persistent_grid();
+#define NB200_NUM(TEAM, SUB, TLOG, SPILL, BIN)                                                                   \
+    spgemm_numeric_kernel<T, I, TEAM, SUB, TLOG, SPILL><<<g, 256, 0, st>>>(                                       \
+        w.lists + (int64_t)(BIN) * A_rows, w.header + 8 + (BIN), A_data, A_indices, A_indptr, B_data, B_indices, \
+        B_indptr, w.row_nnz, w.spill_off, spill_keys, spill_vals, spill_slots, w.header, C_indptr, C_indices, C_data)
+    NB200_NUM(8, 1, 6, false, 0);
+    NB200_NUM(32, 4, 9, false, 1);
+    NB200_NUM(256, 32, 12, false, 2);
+    NB200_NUM(256, 32, 0, true, 3);
+#undef NB200_NUM
+    return launch_status();
+}
+
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" size_t nb200_spgemm_workspace_bytes(int64_t A_rows) { return spgemm_workspace_bytes(A_rows); }
+
+extern "C" int nb200_spgemm_plan(int64_t A_rows, int64_t A_cols, int64_t A_nnz,
+                                 const void* A_indices, const void* A_indptr, const void* B_indptr, int itype,
+                                 void* workspace, size_t workspace_bytes, nb200_stream stream) {
+    (void)A_cols;
+    if (A_rows < 0 || A_nnz < 0 || !workspace) return NB200_ERR_BAD_ARG;
+    if (A_rows >= 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
+    if (A_rows > 0 && (!A_indptr || !B_indptr || (A_nnz > 0 && !A_indices))) return NB200_ERR_BAD_ARG;
+    return NB200_DISPATCH_I(itype,
+        (spgemm_plan<I>(A_rows, (const I*)A_indices, (const I*)A_indptr, (const I*)B_indptr, workspace, workspace_bytes,
+                        as_stream(stream))));
+}
+
+extern "C" int nb200_spgemm_symbolic(int64_t A_rows, int64_t A_cols, int64_t B_cols,
+                                     const void* A_indices, const void* A_indptr,
+                                     const void* B_indices, const void* B_indptr, int itype,
+                                     void* workspace, size_t workspace_bytes, void* spill, int64_t spill_slots,
+                                     int64_t* C_indptr, nb200_stream stream) {
+    (void)A_cols;
+    if (A_rows < 0 || B_cols < 0 || !workspace || !C_indptr || spill_slots < 0) return NB200_ERR_BAD_ARG;
+    if (B_cols >= 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
+    return NB200_DISPATCH_I(itype,
+        (spgemm_symbolic<I>(A_rows, (const I*)A_indices, (const I*)A_indptr, (const I*)B_indices, (const I*)B_indptr,
+                            workspace, workspace_bytes, (uint32_t*)spill, spill_slots, C_indptr, as_stream(stream))));
+}
+
+extern "C" int nb200_spgemm_numeric(int64_t A_rows, int64_t A_cols, int64_t B_cols,
+                                    const void* A_data, const void* A_indices, const void* A_indptr,
+                                    const void* B_data, const void* B_indices, const void* B_indptr,
+                                    int dtype, int itype, void* workspace, size_t workspace_bytes,
+                                    void* spill, int64_t spill_slots,
+                                    const int64_t* C_indptr, int64_t* C_indices, void* C_data, nb200_stream stream) {
+    (void)A_cols; (void)B_cols;
+    if (A_rows < 0 || !workspace || !C_indptr || spill_slots < 0) return NB200_ERR_BAD_ARG;
+    return NB200_DISPATCH(dtype, itype,
+        (spgemm_numeric<T, I>(A_rows, (const T*)A_data, (const I*)A_indices, (const I*)A_indptr,
+                              (const T*)B_data, (const I*)B_indices, (const I*)B_indptr, workspace, workspace_bytes,
+                              spill, spill_slots, C_indptr, C_indices, (T*)C_data, as_stream(stream))));
+}
+
+extern "C" int nb200_spgemm_backward(int64_t A_rows, int64_t A_cols, int64_t A_nnz,
+                                     const void* A_data, const void* A_indices, const void* A_indptr,
+                                     const void* At_indptr, const void* At_indices, const void* At_perm,
+                                     int64_t B_rows, int64_t B_cols, int64_t B_nnz,
+                                     const void* B_data, const void* B_indices, const void* B_indptr,
+                                     const void* grad_C, const int64_t* C_indices, const int64_t* C_indptr,
+                                     void* grad_A, void* grad_B, int dtype, int itype, nb200_stream stream) {
+    (void)A_cols; (void)B_cols;
+    if (A_rows < 0 || A_nnz < 0 || B_rows < 0 || B_nnz < 0) return NB200_ERR_BAD_ARG;
+    if ((A_nnz > 0 && (!A_data || !A_indices || !A_indptr || !grad_A || !At_indptr || !At_indices || !At_perm)) ||
+        (B_nnz > 0 && (!B_data || !B_indices || !B_indptr || !grad_B)) || !C_indptr)
+        return NB200_ERR_BAD_ARG;
+    cudaStream_t st = as_stream(stream);
+    return NB200_DISPATCH(dtype, itype, ([&]() -> int {
+        if (A_nnz > 0)
+            spgemm_grad_A_kernel<T, I><<<flat_grid(A_nnz), 256, 0, st>>>(
+                A_rows, A_nnz, (const I*)A_indices, (const I*)A_indptr, (const T*)B_data, (const I*)B_indices,
+                (const I*)B_indptr, (const T*)grad_C, C_indices, C_indptr, (T*)grad_A);
+        if (B_nnz > 0)
+            spgemm_grad_B_kernel<T, I><<<flat_grid(B_nnz), 256, 0, st>>>(
+                B_rows, B_nnz, (const I*)B_indices, (const I*)B_indptr, (const T*)A_data, (const I*)At_indptr,
+                (const I*)At_indices, (const I*)At_perm, (const T*)grad_C, C_indices, C_indptr, (T*)grad_B);
+        return launch_status();
+    }()));
+}

@@ -179,3 +179,76 @@ def spdmm_backward(A_rows, A_cols, A_data, A_indices, A_indptr, B, grad_C):
         _cabi.call("nb200_spdmm_forward", A_cols, A_rows, K, plan.nnz, _ptr(A_data), _ptr(t_indices), _ptr(t_indptr),
                    _ptr(t_perm), _ptr(G), _ptr(grad_B), code, itype, _stream())
     return [grad_A, grad_B]
+
+
+# -------------------------------------------------------------------------------------------------
+# SpGEMM                                             reference cpp/sparse_csr.hpp:45-54
+# -------------------------------------------------------------------------------------------------
+def _common_width(plan_a, plan_b):
+    """CSR arrays of both operands in one index width (int32 only if both patterns fit)."""
+    if plan_a.fits_int32() and plan_b.fits_int32():
+        ai, ap, itype = plan_a.csr()
+        bi, bp, _ = plan_b.csr()
+        return ai, ap, bi, bp, itype
+    return plan_a.indices, plan_a.indptr, plan_b.indices, plan_b.indptr, _cabi.I64
+
+
+def _header(work):
+    """The 16-word int64 header at the start of an SpGEMM workspace (device-to-host copy, syncs)."""
+    return work[:128].view(torch.int64).cpu()
+
+
+def spgemm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B_rows, B_cols, B_data, B_indices, B_indptr):
+    dev = _require_cuda(A_data, A_indices, A_indptr, B_data, B_indices, B_indptr)
+    A_data = _values(A_data)
+    B_data = _values(B_data, A_data)
+    plan_a = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
+    plan_b = _plan.get_plan(B_rows, B_cols, _index_tensor(B_indices), _index_tensor(B_indptr))
+    ai, ap, bi, bp, itype = _common_width(plan_a, plan_b)
+    code = _dtype_code(A_data)
+    vbytes = A_data.element_size()
+    with torch.cuda.device(dev):
+        wbytes = _cabi.lib().nb200_spgemm_workspace_bytes(A_rows)
+        work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+        _cabi.call("nb200_spgemm_plan", A_rows, A_cols, plan_a.nnz, _ptr(ai), _ptr(ap), _ptr(bp), itype,
+                   _ptr(work), wbytes, _stream())
+        slots = int(_header(work)[4])
+        spill = torch.empty(slots * 4, dtype=torch.uint8, device=dev) if slots else None
+        C_indptr = torch.empty(A_rows + 1, dtype=torch.int64, device=dev)
+        _cabi.call("nb200_spgemm_symbolic", A_rows, A_cols, B_cols, _ptr(ai), _ptr(ap), _ptr(bi), _ptr(bp), itype,
+                   _ptr(work), wbytes, _ptr(spill), slots, _ptr(C_indptr), _stream())
+        head = _header(work)
+        if int(head[14]) != 0:
+            raise RuntimeError("nb200_spgemm_symbolic: spill area too small")
+        nnz_c, slots = int(head[13]), int(head[12])
+        spill = torch.empty(slots * (vbytes + 4), dtype=torch.uint8, device=dev) if slots else None
+        C_indices = torch.empty(nnz_c, dtype=torch.int64, device=dev)
+        C_data = torch.empty(nnz_c, dtype=A_data.dtype, device=dev)
+        _cabi.call("nb200_spgemm_numeric", A_rows, A_cols, B_cols, _ptr(A_data), _ptr(ai), _ptr(ap),
+                   _ptr(B_data), _ptr(bi), _ptr(bp), code, itype, _ptr(work), wbytes, _ptr(spill), slots,
+                   _ptr(C_indptr), _ptr(C_indices), _ptr(C_data), _stream())
+    return [C_data, C_indices, C_indptr]
+
+
+def spgemm_backward(grad_C, C_indices, C_indptr, A_rows, A_cols, A_data, A_indices, A_indptr,
+                    B_rows, B_cols, B_data, B_indices, B_indptr):
+    dev = _require_cuda(grad_C, C_indices, C_indptr, A_data, A_indices, A_indptr, B_data, B_indices, B_indptr)
+    A_data = _values(A_data)
+    B_data = _values(B_data, A_data)
+    grad_C = _values(grad_C, A_data)
+    C_indices, C_indptr = _index_tensor(C_indices), _index_tensor(C_indptr)
+    plan_a = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
+    plan_b = _plan.get_plan(B_rows, B_cols, _index_tensor(B_indices), _index_tensor(B_indptr))
+    ai, ap, bi, bp, itype = _common_width(plan_a, plan_b)
+    if itype == _cabi.I32:
+        t_indptr, t_indices, t_perm, _ = plan_a.transpose()
+    else:
+        t_indptr, t_indices, t_perm = _plan.transpose_structure(A_rows, A_cols, ai, ap, _cabi.I64, _cabi.I64)
+    with torch.cuda.device(dev):
+        grad_A = torch.empty_like(A_data)
+        grad_B = torch.empty_like(B_data)
+        _cabi.call("nb200_spgemm_backward", A_rows, A_cols, plan_a.nnz, _ptr(A_data), _ptr(ai), _ptr(ap),
+                   _ptr(t_indptr), _ptr(t_indices), _ptr(t_perm), B_rows, B_cols, plan_b.nnz,
+                   _ptr(B_data), _ptr(bi), _ptr(bp), _ptr(grad_C), _ptr(C_indices), _ptr(C_indptr),
+                   _ptr(grad_A), _ptr(grad_B), _dtype_code(A_data), itype, _stream())
+    return [grad_A, grad_B]

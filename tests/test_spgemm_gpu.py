@@ -1,0 +1,121 @@
+"""GPU parity of the hash SpGEMM (symbolic + numeric) and its masked backward: structure must be
+bit-exact (sorted columns, cancelled entries kept), values within tolerance, gradients bit-exact."""
+import pytest
+import torch
+
+from parity import assert_close, assert_same, case, case_names
+from numml_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from numml_b200 import numml_torch_cpp
+    return numml_torch_cpp
+
+
+def run_case(ops, A, B, grad_C=None):
+    (ad, ai, ap, (am, an)), (bd, bi, bp, (bm, bn)) = A, B
+    dA = [t.cuda() for t in (ad, ai, ap)]
+    dB = [t.cuda() for t in (bd, bi, bp)]
+    Cd, Ci, Cp = ops.spgemm_forward(am, an, *dA, bm, bn, *dB)
+    grads = None
+    if grad_C is not None:
+        grads = ops.spgemm_backward(grad_C.cuda(), Ci, Cp, am, an, *dA, bm, bn, *dB)
+    return (Cd, Ci, Cp), grads
+
+
+def test_golden_spgemm(golden_ops, ops):
+    for name in case_names(golden_ops, "spgemm_"):
+        c = case(golden_ops, name)
+        A = (c["A_data"], c["A_indices"], c["A_indptr"], (int(c["A_shape"][0]), int(c["A_shape"][1])))
+        B = (c["B_data"], c["B_indices"], c["B_indptr"], (int(c["B_shape"][0]), int(c["B_shape"][1])))
+        (Cd, Ci, Cp), (gA, gB) = run_case(ops, A, B, c["grad_C"])
+        assert_same(c["C_indptr"], Cp, name + " indptr")
+        assert_same(c["C_indices"], Ci, name + " indices")
+        assert_close(c["C_data"], Cd, name + " data") if c["C_data"].abs().sum() > 0 else assert_same(c["C_data"], Cd, name)
+        assert_same(c["grad_A"], gA, name + " grad_A")
+        assert_same(c["grad_B"], gB, name + " grad_B")
+
+
+def test_cancelled_entry_is_kept(ops):
+    one = (torch.tensor([1., 1.], dtype=torch.float64), torch.tensor([0, 1]), torch.tensor([0, 2]), (1, 2))
+    col = (torch.tensor([1., -1.], dtype=torch.float64), torch.tensor([0, 0]), torch.tensor([0, 1, 2]), (2, 1))
+    (Cd, Ci, Cp), _ = run_case(ops, one, col)
+    assert Cp.tolist() == [0, 1] and Ci.tolist() == [0] and Cd.tolist() == [0.0]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("shapes,dens", [(((60, 50), (50, 70)), (0.1, 0.1)),      # small rows (8-lane bin)
+                                          (((300, 400), (400, 500)), (0.04, 0.05)),  # 32-lane bin
+                                          (((40, 600), (600, 3000)), (0.3, 0.05)),   # CTA bin
+                                          (((6, 900), (900, 20000)), (0.9, 0.02)),   # global-memory spill bin
+                                          (((1, 1), (1, 1)), (1.0, 1.0))])
+def test_random_vs_oracle(oracle, ops, dtype, shapes, dens):
+    (am, an), (bm, bn) = shapes
+    A = W.random_csr(am, an, dens[0], seed=5, dtype=dtype)
+    B = W.random_csr(bm, bn, dens[1], seed=6, dtype=dtype)
+    Cd_ref, Ci_ref, Cp_ref = oracle.spgemm_forward(am, an, *A[:3], bm, bn, *B[:3])
+    gC = W.randn(Cd_ref.numel(), 7, dtype)
+    gA_ref, gB_ref = oracle.spgemm_backward(gC, Ci_ref, Cp_ref, am, an, *A[:3], bm, bn, *B[:3])
+    (Cd, Ci, Cp), (gA, gB) = run_case(ops, A, B, gC)
+    assert_same(Cp_ref, Cp, "C_indptr")
+    assert_same(Ci_ref, Ci, "C_indices")
+    assert_close(Cd_ref, Cd, "C_data")
+    assert_same(gA_ref, gA, "grad_A")
+    assert_same(gB_ref, gB, "grad_B")
+
+
+def test_empty_operands(ops):
+    z = (torch.zeros(0, dtype=torch.float64), torch.zeros(0, dtype=torch.int64), torch.zeros(5, dtype=torch.int64), (4, 3))
+    B = W.random_csr(3, 6, 0.5, seed=1, dtype=torch.float64, empty_rows=False)
+    (Cd, Ci, Cp), (gA, gB) = run_case(ops, z, B, torch.zeros(0, dtype=torch.float64))
+    assert Cd.numel() == 0 and Ci.numel() == 0 and Cp.tolist() == [0] * 5
+    assert gA.numel() == 0 and torch.all(gB == 0)
+
+
+def test_galerkin_product_vs_oracle(oracle, ops):
+    """A*A and (P^T A) P on a 2-D Laplacian with 2x2 aggregation: the AMG products of the benchmark
+    configuration, at a size the CPU oracle finishes quickly."""
+    n = 48
+    A = W.poisson2d_5pt(n, torch.float64)
+    P = W.aggregation_2x2(n, torch.float64)
+    am, an = A[3]
+    pm, pn = P[3]
+    # C = A A
+    ref = oracle.spgemm_forward(am, an, *A[:3], am, an, *A[:3])
+    assert ref[0].numel() == 13 * n * n - 20 * n + 4
+    (Cd, Ci, Cp), _ = run_case(ops, A, A)
+    assert_same(ref[2], Cp, "AA indptr"); assert_same(ref[1], Ci, "AA indices"); assert_close(ref[0], Cd, "AA data")
+    # Pt = P^T, then (Pt A) P
+    Pt_ref = oracle.csr_transpose_forward(pm, pn, *P[:3])
+    Pt = (Pt_ref[0], Pt_ref[1], Pt_ref[2], (pn, pm))
+    PtA_ref = oracle.spgemm_forward(pn, pm, *Pt[:3], am, an, *A[:3])
+    PtA = (PtA_ref[0], PtA_ref[1], PtA_ref[2], (pn, an))
+    Ac_ref = oracle.spgemm_forward(pn, an, *PtA[:3], pm, pn, *P[:3])
+    (d1, i1, p1), _ = run_case(ops, Pt, A)
+    assert_same(PtA_ref[2], p1, "PtA indptr"); assert_same(PtA_ref[1], i1, "PtA indices"); assert_close(PtA_ref[0], d1, "PtA data")
+    gC = W.randn(Ac_ref[0].numel(), 3, torch.float64)
+    (d2, i2, p2), (gA, gB) = run_case(ops, PtA, P, gC)
+    assert_same(Ac_ref[2], p2, "Ac indptr"); assert_same(Ac_ref[1], i2, "Ac indices"); assert_close(Ac_ref[0], d2, "Ac data")
+    gA_ref, gB_ref = oracle.spgemm_backward(gC, Ac_ref[1], Ac_ref[2], pn, an, *PtA[:3], pm, pn, *P[:3])
+    assert_same(gA_ref, gA, "grad PtA"); assert_same(gB_ref, gB, "grad P")
+
+
+def test_structure_properties_at_scale(ops):
+    """Benchmark-scale A*A (2-D Laplacian, 1024^2 grid): nnz matches the closed form 13n^2-20n+4,
+    every row is strictly ascending, and (A A) 1 == A (A 1)."""
+    n = 1024
+    A = W.poisson2d_5pt(n, torch.float64)
+    m = n * n
+    (Cd, Ci, Cp), _ = run_case(ops, A, A)
+    assert int(Cp[-1]) == 13 * n * n - 20 * n + 4 == Ci.numel()
+    rows = torch.repeat_interleave(torch.arange(m, device="cuda"), Cp[1:] - Cp[:-1])
+    key = rows * m + Ci
+    assert torch.all(key[1:] > key[:-1])
+    ones = torch.ones(m, dtype=torch.float64, device="cuda")
+    dA = [t.cuda() for t in A[:3]]
+    lhs = ops.spgemv_forward(m, m, Cd, Ci, Cp, ones)
+    rhs = ops.spgemv_forward(m, m, *dA, ops.spgemv_forward(m, m, *dA, ones))
+    assert torch.allclose(lhs, rhs, atol=1e-12)
