@@ -199,6 +199,52 @@ NB200_API int nb200_spgemm_backward(int64_t A_rows, int64_t A_cols, int64_t A_nn
                                     const void* grad_C, const int64_t* C_indices, const int64_t* C_indptr,
                                     void* grad_A, void* grad_B, int dtype, int itype, nb200_stream stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Sparse triangular solve.                         Replaces sptrsv_forward (reference
+ * cpp/sparse_csr.hpp:94-98, CPU cpp/sparse_csr_cpu.cpp:652-723, CUDA cpp/sparse_csr_cuda.cu:714-831)
+ * and, with the two helpers below, sptrsv_backward (cpp/sparse_csr.hpp:100-105, CPU :725-759,
+ * CUDA :833-860).
+ *
+ * nb200_sptrsv_analyse   once per pattern and triangle: computes the dependency levels by frontier
+ *                        peeling and writes `order` (n int32: rows sorted by level, then by row).
+ *                        Needs the transposed structure of the matrix (t_indptr, t_indices; see
+ *                        nb200_csr_transpose_structure) and columns sorted within each row.  The
+ *                        number of levels is written to the HOST word *nlevels_host.  This call
+ *                        synchronises `stream` (it polls a completion flag between batches of level
+ *                        kernels); no kernel in it waits on another kernel.
+ * nb200_sptrsv_solve     x = A^{-1} b for `nrhs` right-hand sides stored row-major [n, nrhs] (nrhs = 1
+ *                        is the reference's single-vector call).  Substitution is done in double and
+ *                        rounded to the value type at the end, entries are accumulated in the
+ *                        reference's order with unfused multiply and add: the result is bit-identical
+ *                        to the reference CPU loop.  `perm` (may be NULL) reads entry k's value as
+ *                        data[perm[k]], which is how the transposed system of the backward pass is
+ *                        solved from the cached transposed structure.  `x_double` (n*nrhs doubles) is
+ *                        required when dtype is NB200_F32 (for NB200_F64 the solve works in `x`).
+ *                        The working array is pre-filled with an all-ones bit pattern that marks
+ *                        "not solved yet"; a result that would equal it is stored as the canonical NaN.
+ *                        Lanes wait for the unknowns they depend on with a bounded poll: when
+ *                        `wait_budget_cycles` SM cycles (<= 0: 2e9, about a second) pass without
+ *                        progress the kernel stores NB200_ERR_WAIT_BUDGET in the device word `status`
+ *                        (which the caller zeroes beforehand and reads afterwards), writes NaN into the
+ *                        affected rows and returns; it never spins without a limit.
+ * nb200_masked_outer     out[k] = sum_r alpha * (a[row(k), r] * b[col(k), r]): the masked outer
+ *                        product grad_A = -(grad_b x^T) on the pattern of A (alpha = -1), summed over
+ *                        the right-hand sides in ascending order.
+ * ------------------------------------------------------------------------------------------- */
+NB200_API size_t nb200_sptrsv_analysis_workspace_bytes(int64_t n);
+NB200_API int nb200_sptrsv_analyse(int64_t n, int64_t nnz, const void* indices, const void* indptr,
+                                   const void* t_indptr, const void* t_indices, int itype, int lower,
+                                   int32_t* order, int64_t* nlevels_host,
+                                   void* workspace, size_t workspace_bytes, nb200_stream stream);
+NB200_API int nb200_sptrsv_solve(int64_t n, int64_t nnz, int64_t nrhs,
+                                 const void* data, const void* indices, const void* indptr, const void* perm,
+                                 const int32_t* order, int lower, int unit, const void* b, void* x,
+                                 double* x_double, int32_t* status, int64_t wait_budget_cycles,
+                                 int dtype, int itype, nb200_stream stream);
+NB200_API int nb200_masked_outer(int64_t rows, int64_t nnz, int64_t nrhs, const void* indices, const void* indptr,
+                                 const void* a, const void* b, double alpha, void* out,
+                                 int dtype, int itype, nb200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -34,6 +34,11 @@ SIGNATURES = {
                                     _vp, _vp, _vp, _vp]),
     "nb200_spgemm_backward": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp,
                                      _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
+    "nb200_sptrsv_analysis_workspace_bytes": (_sz, [_i64]),
+    "nb200_sptrsv_analyse": (_int, [_i64, _i64, _vp, _vp, _vp, _vp, _int, _int, _vp, _vp, _vp, _sz, _vp]),
+    "nb200_sptrsv_solve": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp, _vp, _vp, _vp, _i64,
+                                  _int, _int, _vp]),
+    "nb200_masked_outer": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _c.c_double, _vp, _int, _int, _vp]),
     "nb200_spdmm_backward_grad_A": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
 }
 

@@ -68,6 +68,29 @@ class PatternPlan:
         return self._t
 
 
+    # -- triangular-solve schedules ----------------------------------------------------------------
+    def sptrsv_order(self, lower, transposed=False):
+        """(order, nlevels) for solving with this pattern (``transposed=False``) or with its
+        transpose (``transposed=True``; the triangle given is that of the transposed matrix)."""
+        key = ("sptrsv", bool(lower), bool(transposed))
+        if key not in self.extra:
+            idx, ptr, itype = self.csr()
+            t_indptr, t_indices, _, _ = self.transpose()
+            if transposed:
+                idx, ptr, t_indices, t_indptr = t_indices, t_indptr, idx, ptr
+            n = self.rows
+            dev = self.indices.device
+            with torch.cuda.device(dev):
+                order = torch.empty(n, dtype=torch.int32, device=dev)
+                wbytes = _cabi.lib().nb200_sptrsv_analysis_workspace_bytes(n)
+                work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+                nlevels = ctypes.c_int64(0)
+                _cabi.call("nb200_sptrsv_analyse", n, self.nnz, _ptr(idx), _ptr(ptr), _ptr(t_indptr), _ptr(t_indices),
+                           itype, int(bool(lower)), _ptr(order), ctypes.byref(nlevels), _ptr(work), wbytes, _stream())
+            self.extra[key] = (order, int(nlevels.value))
+        return self.extra[key]
+
+
 def transpose_structure(rows, cols, indices, indptr, itype_in, itype_out):
     """Run nb200_csr_transpose_structure; returns (t_indptr, t_indices, t_perm)."""
     nnz = int(indices.numel())

@@ -1,0 +1,344 @@
+// Sparse triangular solve (forward and the pieces of its backward) for CSR on sm_100a.
+//
+// Analysis (once per sparsity pattern and triangle): dependency levels by frontier peeling
+// (Kahn): a row is ready when every strictly-triangular entry of it refers to a solved row.
+// One small kernel per level walks the current frontier through the transposed structure and
+// decrements the in-degree of the dependents; no kernel ever waits on another.  Rows are then
+// sorted by (level, row) into `order`.
+//
+// Solve: one launch.  Row order[p] is owned by the p-th team (a team is as many lanes as there
+// are right-hand sides, up to 32, so a dependency x[j, :] is read as one contiguous line).
+// Because `order` is topological, the rows a team needs belong to teams with a smaller global
+// index, i.e. to CTAs that were dispatched earlier; each lane polls the solution words it needs
+// (the solution array itself is the ready flag, see below).  Every poll loop is bounded by a
+// cycle budget and by a shared abort word: on expiry the kernel records NB200_ERR_WAIT_BUDGET in
+// the status word, writes NaN for its own unknowns and returns, and every other waiter sees the
+// abort word and leaves too.
+//
+// Arithmetic follows the reference: substitution in double whatever the value type, entries
+// accumulated in storage order (ascending for a lower solve, descending from the row end for an
+// upper solve) with unfused multiply and add, scan of a row stopped at the first entry on the
+// wrong side of the diagonal, stored diagonal ignored with `unit`.  Results are bit-identical to
+// the reference CPU loop.
+#include "primitives.cuh"
+
+namespace nb200 {
+
+// ---------------------------------------------------------------------------------------------
+// Analysis kernels
+// ---------------------------------------------------------------------------------------------
+// counters: [0..2] rotating frontier sizes, [3] rows finished, [4] number of levels, [5] done flag
+template <typename I>
+__global__ void sptrsv_indegree_kernel(int64_t n, const I* __restrict__ indices, const I* __restrict__ indptr,
+                                       bool lower, int32_t* __restrict__ indeg, int32_t* __restrict__ frontier,
+                                       int32_t* __restrict__ counters) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        int32_t deps = 0;
+        for (int64_t k = (int64_t)indptr[i]; k < (int64_t)indptr[i + 1]; ++k) {
+            const int64_t j = (int64_t)indices[k];
+            deps += lower ? (j < i) : (j > i);
+        }
+        indeg[i] = deps;
+        if (deps == 0) frontier[atomicAdd(counters + 0, 1)] = (int32_t)i;
+    }
+}
+
+template <typename I>
+__global__ void sptrsv_kahn_kernel(int32_t level, bool lower, const I* __restrict__ t_indptr,
+                                   const I* __restrict__ t_indices, const int32_t* __restrict__ frontier_in,
+                                   int32_t* __restrict__ frontier_out, int32_t* __restrict__ indeg,
+                                   uint32_t* __restrict__ level_of, int32_t* __restrict__ counters) {
+    const int32_t n_in = counters[level % 3];
+    int32_t* n_out = counters + (level + 1) % 3;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        counters[(level + 2) % 3] = 0;   // next kernel's output counter
+        if (n_in == 0) {
+            if (counters[5] == 0) { counters[4] = level; counters[5] = 1; }
+        } else {
+            counters[3] += n_in;
+        }
+    }
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; f < n_in; f += stride) {
+        const int64_t j = frontier_in[f];
+        level_of[j] = (uint32_t)level;
+        for (int64_t a = (int64_t)t_indptr[j]; a < (int64_t)t_indptr[j + 1]; ++a) {
+            const int64_t i = (int64_t)t_indices[a];     // entry (i, j) of the matrix
+            if (lower ? (i > j) : (i < j)) {
+                if (atomicSub(indeg + i, 1) == 1) frontier_out[atomicAdd(n_out, 1)] = (int32_t)i;
+            }
+        }
+    }
+}
+
+__global__ void sptrsv_iota_kernel(int64_t n, uint32_t* __restrict__ v) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) v[i] = (uint32_t)i;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Solve kernel
+// ---------------------------------------------------------------------------------------------
+// The double-precision solution array doubles as the ready flag: it is filled with an all-ones
+// bit pattern (a NaN no arithmetic produces) before the launch, and a lane that needs x[j, c]
+// simply re-reads that one 8-byte word through L2 until it differs.  One round trip delivers both
+// "ready" and the value, and no fence is needed because nothing else has to be ordered with it.
+constexpr long long kNotReady = -1LL;                                  // 0xffff'ffff'ffff'ffff
+
+__device__ __forceinline__ long long ld_relaxed_bits(const double* p) {
+    long long v;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int ld_relaxed_s32(const int32_t* p) {
+    int v;
+    asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+template <typename T, typename I, int TS, bool PERM>
+__global__ void __launch_bounds__(256)
+sptrsv_syncfree_kernel(int64_t n, int64_t nrhs, const T* __restrict__ data, const I* __restrict__ indices,
+                       const I* __restrict__ indptr, const I* __restrict__ perm,
+                       const int32_t* __restrict__ order, bool lower, bool unit,
+                       const T* __restrict__ b, T* __restrict__ x, double* __restrict__ xd,
+                       int32_t* __restrict__ status, long long budget) {
+    constexpr int D = 8;                                   // dependencies polled together
+    const int tl = threadIdx.x % TS;
+    const int64_t pos = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / TS;
+    if (pos >= n) return;
+    const int64_t i = (int64_t)order[pos];
+    const int64_t s = (int64_t)indptr[i], len = (int64_t)indptr[i + 1] - s;
+    const double canonical_nan = __longlong_as_double(0x7ff8000000000000LL);
+    bool ok = true;
+
+    for (int64_t c = tl; c < nrhs; c += TS) {              // this lane's right-hand sides
+        double acc = 0.0, diag = 0.0;
+        bool stop = false;
+        // lower: ascending from the row start; upper: descending from the row end
+        for (int64_t q = 0; q < len && !stop && ok; q += D) {
+            int64_t jj[D];
+            double aa[D], xv[D];
+            unsigned valid = 0, pend = 0;
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                jj[d] = i; aa[d] = 0.0; xv[d] = 0.0;
+                if (!stop && q + d < len) {
+                    const int64_t k = lower ? (s + q + d) : (s + len - 1 - q - d);
+                    const int64_t j = (int64_t)indices[k];
+                    if (lower ? (j > i) : (j < i)) {
+                        stop = true;
+                    } else {
+                        jj[d] = j;
+                        aa[d] = (double)(PERM ? data[(int64_t)perm[k]] : data[k]);
+                        valid |= 1u << d;
+                        if (j != i) pend |= 1u << d;
+                    }
+                }
+            }
+            long long t0 = 0;
+            for (unsigned spins = 0; pend != 0; ++spins) {
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    if ((pend >> d) & 1u) {
+                        const long long bits = ld_relaxed_bits(xd + jj[d] * nrhs + c);
+                        if (bits != kNotReady) { xv[d] = __longlong_as_double(bits); pend &= ~(1u << d); }
+                    }
+                }
+                if (pend != 0) {
+                    if (spins == 0) t0 = clock64();
+                    if ((spins & 31u) == 31u) {
+                        if (ld_relaxed_s32(status) != 0) { ok = false; break; }
+                        if (clock64() - t0 > budget) { atomicExch(status, (int)NB200_ERR_WAIT_BUDGET); ok = false; break; }
+                    }
+                }
+            }
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                if ((valid >> d) & 1u) {
+                    if (jj[d] == i) diag = aa[d];
+                    else acc = __dadd_rn(acc, __dmul_rn(aa[d], xv[d]));
+                }
+            }
+        }
+        double xi;
+        if (ok) {
+            xi = (double)b[i * nrhs + c] - acc;
+            if (!unit) xi /= diag;
+            if (__double_as_longlong(xi) == kNotReady) xi = canonical_nan;   // never publish the marker itself
+        } else {
+            xi = canonical_nan;                                              // marks an aborted solve
+        }
+        __stcg(xd + i * nrhs + c, xi);
+        if ((const void*)xd != (const void*)x) x[i * nrhs + c] = (T)xi;
+    }
+}
+
+// out[k] = sum over r of alpha * (a[row(k), r] * b[col(k), r]), r ascending
+template <typename T, typename I>
+__global__ void masked_outer_kernel(int64_t rows, int64_t nnz, int64_t nrhs, const I* __restrict__ indices,
+                                    const I* __restrict__ indptr, const T* __restrict__ a, const T* __restrict__ b,
+                                    T alpha, T* __restrict__ out) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < nnz; k += stride) {
+        int64_t lo = 0, hi = rows;
+        while (hi - lo > 1) {
+            const int64_t mid = (lo + hi) >> 1;
+            if ((int64_t)indptr[mid] <= k) lo = mid; else hi = mid;
+        }
+        const int64_t j = (int64_t)indices[k];
+        const T* ar = a + lo * nrhs;
+        const T* br = b + j * nrhs;
+        T s = mul_rn(alpha, mul_rn(ldg(ar), ldg(br)));
+        for (int64_t r = 1; r < nrhs; ++r) s = add_rn(s, mul_rn(alpha, mul_rn(ldg(ar + r), ldg(br + r))));
+        out[k] = s;
+    }
+}
+
+static inline unsigned flat_grid(int64_t n) {
+    const int64_t want = ceil_div(n > 0 ? n : 1, (int64_t)256);
+    return (unsigned)(want > (int64_t)kSMs * 32 ? (int64_t)kSMs * 32 : want);
+}
+
+static inline int bit_length(int64_t v) {
+    int bits = 0;
+    while (v > 0) { ++bits; v >>= 1; }
+    return bits;
+}
+
+static size_t analysis_workspace_bytes(int64_t n) {
+    const size_t m = (size_t)(n > 0 ? n : 1);
+    // indeg, two frontiers, level keys a/b, row ids a/b, counters, sort scratch
+    return 7 * Workspace::pad(m * sizeof(int32_t)) + Workspace::pad(8 * sizeof(int32_t)) + Workspace::pad(sort_scratch_bytes(n));
+}
+
+template <typename I>
+int sptrsv_analyse(int64_t n, const I* indices, const I* indptr, const I* t_indptr, const I* t_indices, bool lower,
+                   int32_t* order, int64_t* nlevels_host, void* workspace, size_t bytes, cudaStream_t st) {
+    *nlevels_host = 0;
+    if (n == 0) return NB200_OK;
+    const size_t m = (size_t)n;
+    Workspace ws(workspace, bytes);
+    int32_t* indeg = ws.take<int32_t>(m);
+    int32_t* front[2] = {ws.take<int32_t>(m), ws.take<int32_t>(m)};
+    uint32_t* key_a = ws.take<uint32_t>(m);
+    uint32_t* key_b = ws.take<uint32_t>(m);
+    uint32_t* val_a = ws.take<uint32_t>(m);
+    uint32_t* val_b = ws.take<uint32_t>(m);
+    int32_t* counters = ws.take<int32_t>(8);
+    const size_t ssb = sort_scratch_bytes(n);
+    char* sscratch = ws.take<char>(ssb);
+    if (!ws.ok()) return NB200_ERR_WORKSPACE;
+
+    if (cudaMemsetAsync(counters, 0, 8 * sizeof(int32_t), st) != cudaSuccess) return NB200_ERR_CUDA;
+    // rows that are never reached (cannot happen for a triangular dependency graph) keep level 0
+    if (cudaMemsetAsync(key_a, 0, m * sizeof(uint32_t), st) != cudaSuccess) return NB200_ERR_CUDA;
+    sptrsv_indegree_kernel<I><<<flat_grid(n), 256, 0, st>>>(n, indices, indptr, lower, indeg, front[0], counters);
+
+    const unsigned kgrid = (unsigned)(kSMs * 2);
+    int32_t host_counters[8] = {0};
+    int32_t level = 0;
+    const int32_t chunk = 128;
+    while (true) {
+        for (int32_t q = 0; q < chunk; ++q, ++level)
+            sptrsv_kahn_kernel<I><<<kgrid, 256, 0, st>>>(level, lower, t_indptr, t_indices, front[level & 1],
+                                                       front[(level + 1) & 1], indeg, key_a, counters);
+        if (cudaMemcpyAsync(host_counters, counters, sizeof(host_counters), cudaMemcpyDeviceToHost, st) != cudaSuccess)
+            return NB200_ERR_CUDA;
+        if (cudaStreamSynchronize(st) != cudaSuccess) return NB200_ERR_CUDA;
+        if (host_counters[5] != 0) break;
+        if ((int64_t)level > n + chunk) return NB200_ERR_PRECONDITION;   // cannot need more levels than rows
+    }
+    if ((int64_t)host_counters[3] != n) return NB200_ERR_PRECONDITION;
+    const int64_t nlevels = host_counters[4];
+    *nlevels_host = nlevels;
+
+    sptrsv_iota_kernel<<<flat_grid(n), 256, 0, st>>>(n, val_a);
+    bool in_a = true;
+    int rc = sort_pairs_u32(n, bit_length(nlevels - 1), key_a, val_a, key_b, val_b, &in_a, sscratch, ssb, st);
+    if (rc != NB200_OK) return rc;
+    if (cudaMemcpyAsync(order, in_a ? val_a : val_b, m * sizeof(int32_t), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+        return NB200_ERR_CUDA;
+    return launch_status();
+}
+
+template <typename T, typename I, bool PERM>
+int sptrsv_solve_team(int ts, int64_t n, int64_t nrhs, const T* data, const I* indices, const I* indptr, const I* perm,
+                      const int32_t* order, bool lower, bool unit, const T* b, T* x, double* xd,
+                      int32_t* status, long long budget, cudaStream_t st) {
+    const int64_t threads = n * ts;
+    const int64_t grid = ceil_div(threads, (int64_t)256);
+    if (grid > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
+#define NB200_SOLVE(TS_)                                                                                   \
+    sptrsv_syncfree_kernel<T, I, TS_, PERM><<<(unsigned)grid, 256, 0, st>>>(n, nrhs, data, indices, indptr, perm, \
+        order, lower, unit, b, x, xd, status, budget)
+    switch (ts) {
+        case 1: NB200_SOLVE(1); break;
+        case 2: NB200_SOLVE(2); break;
+        case 4: NB200_SOLVE(4); break;
+        case 8: NB200_SOLVE(8); break;
+        case 16: NB200_SOLVE(16); break;
+        default: NB200_SOLVE(32); break;
+    }
+#undef NB200_SOLVE
+    return launch_status();
+}
+
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" size_t nb200_sptrsv_analysis_workspace_bytes(int64_t n) { return analysis_workspace_bytes(n); }
+
+extern "C" int nb200_sptrsv_analyse(int64_t n, int64_t nnz, const void* indices, const void* indptr,
+                                    const void* t_indptr, const void* t_indices, int itype, int lower,
+                                    int32_t* order, int64_t* nlevels_host,
+                                    void* workspace, size_t workspace_bytes, nb200_stream stream) {
+    if (n < 0 || nnz < 0 || !nlevels_host) return NB200_ERR_BAD_ARG;
+    if (n >= 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
+    if (n > 0 && (!indptr || !t_indptr || !order || !workspace || (nnz > 0 && (!indices || !t_indices))))
+        return NB200_ERR_BAD_ARG;
+    return NB200_DISPATCH_I(itype,
+        (sptrsv_analyse<I>(n, (const I*)indices, (const I*)indptr, (const I*)t_indptr, (const I*)t_indices, lower != 0,
+                           order, nlevels_host, workspace, workspace_bytes, as_stream(stream))));
+}
+
+extern "C" int nb200_sptrsv_solve(int64_t n, int64_t nnz, int64_t nrhs,
+                                  const void* data, const void* indices, const void* indptr, const void* perm,
+                                  const int32_t* order, int lower, int unit, const void* b, void* x,
+                                  double* x_double, int32_t* status, int64_t wait_budget_cycles,
+                                  int dtype, int itype, nb200_stream stream) {
+    if (n < 0 || nnz < 0 || nrhs < 0) return NB200_ERR_BAD_ARG;
+    if (n == 0 || nrhs == 0) return NB200_OK;
+    if (!indptr || !order || !b || !x || !status || (nnz > 0 && (!data || !indices))) return NB200_ERR_BAD_ARG;
+    if (dtype == NB200_F32 && !x_double) return NB200_ERR_BAD_ARG;
+    cudaStream_t st = as_stream(stream);
+    double* xd_all = (dtype == NB200_F64) ? (double*)x : x_double;
+    if (cudaMemsetAsync(xd_all, 0xff, sizeof(double) * (size_t)n * (size_t)nrhs, st) != cudaSuccess) return NB200_ERR_CUDA;
+    int ts = 1;
+    while (ts < 32 && ts < nrhs) ts <<= 1;
+    const long long budget = wait_budget_cycles > 0 ? wait_budget_cycles : 2000000000LL;
+    return NB200_DISPATCH(dtype, itype, ([&]() -> int {
+        double* xd = (dtype == NB200_F64) ? (double*)x : x_double;
+        if (perm)
+            return sptrsv_solve_team<T, I, true>(ts, n, nrhs, (const T*)data, (const I*)indices, (const I*)indptr,
+                                                 (const I*)perm, order, lower != 0, unit != 0, (const T*)b, (T*)x, xd,
+                                                 status, budget, st);
+        return sptrsv_solve_team<T, I, false>(ts, n, nrhs, (const T*)data, (const I*)indices, (const I*)indptr,
+                                              (const I*)perm, order, lower != 0, unit != 0, (const T*)b, (T*)x, xd,
+                                              status, budget, st);
+    }()));
+}
+
+extern "C" int nb200_masked_outer(int64_t rows, int64_t nnz, int64_t nrhs, const void* indices, const void* indptr,
+                                  const void* a, const void* b, double alpha, void* out,
+                                  int dtype, int itype, nb200_stream stream) {
+    if (rows < 0 || nnz < 0 || nrhs < 1) return NB200_ERR_BAD_ARG;
+    if (nnz == 0) return NB200_OK;
+    if (!indices || !indptr || !a || !b || !out) return NB200_ERR_BAD_ARG;
+    return NB200_DISPATCH(dtype, itype,
+        (masked_outer_kernel<T, I><<<flat_grid(nnz), 256, 0, as_stream(stream)>>>(
+             rows, nnz, nrhs, (const I*)indices, (const I*)indptr, (const T*)a, (const T*)b, (T)alpha, (T*)out),
+         launch_status()));
+}

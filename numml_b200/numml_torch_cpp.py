@@ -252,3 +252,86 @@ def spgemm_backward(grad_C, C_indices, C_indptr, A_rows, A_cols, A_data, A_indic
                    _ptr(B_data), _ptr(bi), _ptr(bp), _ptr(grad_C), _ptr(C_indices), _ptr(C_indptr),
                    _ptr(grad_A), _ptr(grad_B), _dtype_code(A_data), itype, _stream())
     return [grad_A, grad_B]
+
+
+# -------------------------------------------------------------------------------------------------
+# Triangular solve                                   reference cpp/sparse_csr.hpp:94-105
+# -------------------------------------------------------------------------------------------------
+# Poll budget of the solve kernel in SM cycles (about a second) and whether every solve reads the
+# device status word back (one small synchronising copy) so that an expired wait raises at once.
+sptrsv_wait_budget_cycles = 2_000_000_000
+sptrsv_check_status = True
+_status_words = {}
+
+
+def _status_word(dev):
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _status_words[key]
+
+
+def check_status(device=None):
+    """Read (and clear) the device status word written by kernels with bounded waits; raises
+    RuntimeError if one of them gave up."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _status_word(dev)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise RuntimeError(f"numml_b200 device status {code}: "
+                           f"{_cabi.lib().nb200_status_string(code).decode()} (results of the affected call hold NaN)")
+
+
+def _solve(plan, data, idx, ptr, perm, itype, order, lower, unit, b):
+    n = plan.rows
+    nrhs = 1 if b.ndim == 1 else int(b.shape[1])
+    dev = b.device
+    x = torch.empty_like(b)
+    xd = torch.empty(n * nrhs, dtype=torch.float64, device=dev) if b.dtype == torch.float32 else None
+    status = _status_word(dev)
+    _cabi.call("nb200_sptrsv_solve", n, plan.nnz, nrhs, _ptr(data), _ptr(idx), _ptr(ptr),
+               _ptr(perm) if perm is not None else None, _ptr(order), int(bool(lower)), int(bool(unit)),
+               _ptr(b), _ptr(x), _ptr(xd) if xd is not None else None, _ptr(status),
+               int(sptrsv_wait_budget_cycles), _dtype_code(data), itype, _stream())
+    if sptrsv_check_status:
+        check_status(dev)
+    return x
+
+
+def _rhs(b, n, like):
+    if b.ndim not in (1, 2) or b.shape[0] != n:
+        raise RuntimeError(f"right-hand side must have shape ({n},) or ({n}, k), got {tuple(b.shape)}")
+    return _values(b, like)
+
+
+def sptrsv_forward(A_rows, A_cols, A_data, A_indices, A_indptr, lower, unit, b):
+    dev = _require_cuda(A_data, A_indices, A_indptr, b)
+    if A_rows != A_cols:
+        raise RuntimeError(f"triangular solve needs a square matrix, got {A_rows} x {A_cols}")
+    A_data = _values(A_data)
+    b = _rhs(b, A_rows, A_data)
+    plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
+    idx, ptr, itype = plan.csr()
+    with torch.cuda.device(dev):
+        order, _ = plan.sptrsv_order(lower)
+        return _solve(plan, A_data, idx, ptr, None, itype, order, lower, unit, b)
+
+
+def sptrsv_backward(grad_x, x, A_rows, A_cols, A_data, A_indices, A_indptr, lower, unit, b):
+    dev = _require_cuda(grad_x, x, A_data, A_indices, A_indptr)
+    A_data = _values(A_data)
+    grad_x = _rhs(grad_x, A_rows, A_data)
+    x = _rhs(x, A_rows, A_data)
+    plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
+    idx, ptr, itype = plan.csr()
+    nrhs = 1 if x.ndim == 1 else int(x.shape[1])
+    with torch.cuda.device(dev):
+        t_indptr, t_indices, t_perm, _ = plan.transpose()
+        order_t, _ = plan.sptrsv_order(not lower, transposed=True)
+        # grad_b = A^{-T} grad_x: the opposite-triangle solve on the transposed structure
+        grad_b = _solve(plan, A_data, t_indices, t_indptr, t_perm, itype, order_t, not lower, unit, grad_x)
+        grad_A = torch.empty_like(A_data)
+        _cabi.call("nb200_masked_outer", A_rows, plan.nnz, nrhs, _ptr(idx), _ptr(ptr), _ptr(grad_b), _ptr(x), -1.0,
+                   _ptr(grad_A), _dtype_code(A_data), itype, _stream())
+    return [grad_A, grad_b]
