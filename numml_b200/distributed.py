@@ -1,0 +1,324 @@
+"""Row-block partitioned sparse operators over ``torch.distributed`` (one process per GPU).
+
+The reference has no multi-device path at all; this module adds the one the hot path shards
+along: contiguous row blocks of A (and of every vector / dense operand / second sparse factor),
+with one exchange step per operator:
+
+  * SpMV / SpMM forward: the entries (rows) of x that a rank's columns refer to but another rank
+    owns are packed by the owner and sent point to point; they land in the rank's own memory,
+    behind its local part, before the local kernel runs.  Columns are renumbered to
+    ``[local | halo]`` once, when the partition is built.
+  * SpMV / SpMM backward: grad_A is local; grad_x gets contributions for halo columns, which are
+    sent back to their owners and added in a fixed peer order (deterministic).
+  * SpGEMM: the rows of B that a rank's columns refer to are fetched from their owners (row
+    lengths, then indices and values); the local product's rows concatenate to the single-device
+    result bit for bit, since output rows are independent.
+
+All exchanges are grouped ``isend`` / ``irecv`` calls (NCCL over NVLink on GPUs, gloo on CPU);
+the local compute goes through an operator module with the reference's function names
+(``numml_b200.numml_torch_cpp`` by default), which lets the host logic be exercised on CPU
+ranks with a CPU implementation of the same functions injected by the tests.
+The triangular solve does not shard (its dependency chain spans the matrix).
+"""
+import torch
+import torch.distributed as dist
+
+
+def partition_rows(n, world, indptr=None):
+    """Bounds of ``world`` contiguous row blocks: equal row counts, or equal nonzero counts when
+    the global ``indptr`` is given (for skewed row lengths)."""
+    if indptr is None:
+        return [(n * r) // world for r in range(world + 1)]
+    nnz = int(indptr[-1])
+    targets = torch.tensor([(nnz * r) // world for r in range(1, world)], dtype=indptr.dtype)
+    cuts = torch.searchsorted(indptr, targets, right=False).tolist()
+    bounds = [0] + [min(max(int(c), 0), n) for c in cuts] + [n]
+    for r in range(1, world + 1):
+        bounds[r] = max(bounds[r], bounds[r - 1])
+    return bounds
+
+
+def _take(x, idx):
+    """x[idx] along dim 0 (the pack step of an exchange)."""
+    if x.is_cuda and x.ndim == 1 and x.dtype in (torch.float32, torch.float64):
+        import ctypes
+        from . import _cabi
+        out = torch.empty(idx.numel(), dtype=x.dtype, device=x.device)
+        _cabi.call("nb200_gather", idx.numel(), ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(idx.data_ptr()),
+                   ctypes.c_void_p(out.data_ptr()), _cabi.F64 if x.dtype == torch.float64 else _cabi.F32, _cabi.I64,
+                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        return out
+    return x.index_select(0, idx)
+
+
+class HaloPlan:
+    """Who needs which of my entries, and where the entries I need arrive.
+
+    ``need[p]``  sorted global column ids this rank reads and rank p owns (p != rank)
+    ``send[p]``  local indices (into this rank's block) that rank p reads
+    Halo slot of a needed column = n_local + its rank among all needed columns in ascending
+    global order; since blocks are contiguous and ordered, the slots of one owner are contiguous.
+    """
+
+    def __init__(self, needed_cols, col_bounds, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.col_bounds = list(col_bounds)
+        self.lo, self.hi = self.col_bounds[self.rank], self.col_bounds[self.rank + 1]
+        self.n_local = self.hi - self.lo
+        dev = needed_cols.device
+        bounds_t = torch.tensor(self.col_bounds, dtype=torch.int64, device=dev)
+        owner = torch.searchsorted(bounds_t, needed_cols, right=True) - 1
+        self.halo_cols = needed_cols
+        self.n_halo = int(needed_cols.numel())
+        self.need = [needed_cols[owner == p] for p in range(self.world)]
+        counts = torch.tensor([int(t.numel()) for t in self.need], dtype=torch.int64, device=dev)
+        self.recv_counts = counts.tolist()
+        self.recv_offsets = [0]
+        for c in self.recv_counts:
+            self.recv_offsets.append(self.recv_offsets[-1] + c)
+        # tell every owner how many / which of its entries this rank needs
+        all_counts = [torch.empty_like(counts) for _ in range(self.world)]
+        dist.all_gather(all_counts, counts, group=group)
+        self.send_counts = [int(all_counts[p][self.rank]) for p in range(self.world)]
+        self.send = [torch.empty(self.send_counts[p], dtype=torch.int64, device=dev) for p in range(self.world)]
+        ops = []
+        for p in range(self.world):
+            if p == self.rank:
+                continue
+            if self.recv_counts[p] > 0:
+                ops.append(dist.P2POp(dist.isend, self.need[p].contiguous(), self._peer(p), group=group))
+            if self.send_counts[p] > 0:
+                ops.append(dist.P2POp(dist.irecv, self.send[p], self._peer(p), group=group))
+        self._run(ops)
+        for p in range(self.world):
+            self.send[p] = self.send[p] - self.lo
+        self.peers_in = [p for p in range(self.world) if p != self.rank and self.recv_counts[p] > 0]
+        self.peers_out = [p for p in range(self.world) if p != self.rank and self.send_counts[p] > 0]
+
+    def _peer(self, p):
+        return p if self.group is None else dist.get_global_rank(self.group, p)
+
+    @staticmethod
+    def _run(ops):
+        if ops:
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+
+    def extend(self, x_local):
+        """[x_local | halo entries fetched from their owners], rows along dim 0."""
+        tail = tuple(x_local.shape[1:])
+        x_ext = torch.empty((self.n_local + self.n_halo,) + tail, dtype=x_local.dtype, device=x_local.device)
+        x_ext[:self.n_local] = x_local
+        ops, keep = [], []
+        for p in self.peers_out:
+            buf = _take(x_local, self.send[p])
+            keep.append(buf)
+            ops.append(dist.P2POp(dist.isend, buf, self._peer(p), group=self.group))
+        for p in self.peers_in:
+            a = self.n_local + self.recv_offsets[p]
+            ops.append(dist.P2POp(dist.irecv, x_ext[a:a + self.recv_counts[p]], self._peer(p), group=self.group))
+        self._run(ops)
+        return x_ext
+
+    def reduce(self, g_ext):
+        """Inverse of ``extend`` for gradients: the halo part of g_ext is sent back to the owners
+        and added to their local part (peers in ascending order, so the sum is reproducible)."""
+        g_local = g_ext[:self.n_local].clone()
+        ops, bufs = [], {}
+        for p in self.peers_in:
+            a = self.n_local + self.recv_offsets[p]
+            ops.append(dist.P2POp(dist.isend, g_ext[a:a + self.recv_counts[p]].contiguous(), self._peer(p), group=self.group))
+        for p in self.peers_out:
+            bufs[p] = torch.empty((self.send_counts[p],) + tuple(g_ext.shape[1:]), dtype=g_ext.dtype, device=g_ext.device)
+            ops.append(dist.P2POp(dist.irecv, bufs[p], self._peer(p), group=self.group))
+        self._run(ops)
+        for p in self.peers_out:
+            g_local.index_add_(0, self.send[p], bufs[p])
+        return g_local
+
+
+class _DistMatVec(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, A, data, x_local):
+        x_ext = A.halo.extend(x_local.detach())
+        ctx.A = A
+        ctx.save_for_backward(data, x_ext)
+        n_ext = A.halo.n_local + A.halo.n_halo
+        if x_local.ndim == 1:
+            return A.ops.spgemv_forward(A.n_rows, n_ext, data, A.indices, A.indptr, x_ext)
+        return A.ops.spdmm_forward(A.n_rows, n_ext, data, A.indices, A.indptr, x_ext)
+
+    @staticmethod
+    def backward(ctx, g):
+        A = ctx.A
+        data, x_ext = ctx.saved_tensors
+        n_ext = A.halo.n_local + A.halo.n_halo
+        g = g.contiguous()
+        if x_ext.ndim == 1:
+            grad_A, grad_x_ext = A.ops.spgemv_backward(g, A.n_rows, n_ext, data, A.indices, A.indptr, x_ext)
+        else:
+            grad_A, grad_x_ext = A.ops.spdmm_backward(A.n_rows, n_ext, data, A.indices, A.indptr, x_ext, g)
+        return None, grad_A, A.halo.reduce(grad_x_ext)
+
+
+class DistSparseCSR:
+    """This rank's block of rows of a row-partitioned CSR matrix.
+
+    ``data, indices, indptr`` hold the rows ``row_bounds[rank] .. row_bounds[rank+1]`` with GLOBAL
+    column ids; ``col_bounds`` is the partition of the column space (the partition of x; equal to
+    ``row_bounds`` for a square matrix).  Construction renumbers the columns to
+    ``[local | halo]`` and builds the exchange plan (collective over ``group``).
+    """
+
+    def __init__(self, data, indices, indptr, global_shape, row_bounds, col_bounds=None, group=None, ops=None):
+        if ops is None:
+            from . import numml_torch_cpp as ops
+        self.ops = ops
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.global_shape = tuple(global_shape)
+        self.row_bounds = list(row_bounds)
+        self.col_bounds = list(col_bounds) if col_bounds is not None else list(row_bounds)
+        self.n_rows = self.row_bounds[self.rank + 1] - self.row_bounds[self.rank]
+        lo, hi = self.col_bounds[self.rank], self.col_bounds[self.rank + 1]
+        self.data = data
+        self.global_indices = indices
+        self.indptr = indptr
+        remote = (indices < lo) | (indices >= hi)
+        needed = torch.unique(indices[remote])                    # sorted ascending
+        self.halo = HaloPlan(needed, self.col_bounds, group)
+        local_ids = torch.where(remote, (hi - lo) + torch.searchsorted(needed, indices), indices - lo)
+        self.indices = local_ids.contiguous()
+
+    @property
+    def requires_grad(self):
+        return self.data.requires_grad
+
+    @requires_grad.setter
+    def requires_grad(self, b):
+        self.data.requires_grad = b
+
+    def __matmul__(self, x_local):
+        """A @ x for this rank's rows; ``x_local`` is this rank's block of x (vector or [n, K])."""
+        if isinstance(x_local, DistSparseCSR):
+            return dist_spgemm(self, x_local)
+        return _DistMatVec.apply(self, self.data, x_local)
+
+
+def dist_dot(a, b, group=None):
+    s = torch.dot(a, b)
+    dist.all_reduce(s, group=group)
+    return s
+
+
+def dist_conjugate_gradient(A, b_local, iterations, x_local=None):
+    """Unpreconditioned CG on a row-partitioned SPD matrix with a fixed iteration count (the
+    recurrence of ``numml_b200.krylov.conjugate_gradient``; dot products are all-reduced).
+    Returns this rank's block of the solution and the residual-norm history."""
+    group = A.group
+    x = torch.zeros_like(b_local) if x_local is None else x_local
+    r = b_local.clone() if x_local is None else b_local - (A @ x)
+    p = r.clone()
+    rz = dist_dot(r, r, group)
+    hist = [torch.sqrt(rz)]
+    for _ in range(iterations):
+        Ap = A @ p
+        alpha = rz / dist_dot(Ap, p, group)
+        x = x + alpha * p
+        r = r - alpha * Ap
+        rz_new = dist_dot(r, r, group)
+        p = r + (rz_new / rz) * p
+        rz = rz_new
+        hist.append(torch.sqrt(rz))
+    return x, torch.stack(hist)
+
+
+def _fetch_rows(A, B):
+    """CSR of the rows of B that A's halo columns refer to, fetched from their owners.
+    Returns (data, indices[global cols], indptr) with one row per halo slot of A."""
+    halo = A.halo
+    dev = B.data.device
+    lens_local = (B.indptr[1:] - B.indptr[:-1])
+    lens_ext = halo.extend(lens_local)                       # row lengths of [local | halo] rows
+    halo_lens = lens_ext[halo.n_local:]
+    indptr = torch.zeros(halo.n_halo + 1, dtype=torch.int64, device=dev)
+    indptr[1:] = torch.cumsum(halo_lens, 0)
+    total = int(indptr[-1])
+    data = torch.empty(total, dtype=B.data.dtype, device=dev)
+    indices = torch.empty(total, dtype=torch.int64, device=dev)
+    ops, keep = [], []
+    for p in halo.peers_out:                                 # rows of mine that rank p needs
+        rows = halo.send[p]
+        starts, cnts = B.indptr[rows], lens_local[rows]
+        pos = torch.repeat_interleave(starts - torch.cumsum(cnts, 0) + cnts, cnts) + torch.arange(int(cnts.sum()), device=dev)
+        v, c = B.data.detach()[pos].contiguous(), B.global_indices[pos].contiguous()
+        keep += [v, c]
+        if v.numel() > 0:
+            ops.append(dist.P2POp(dist.isend, v, halo._peer(p), group=halo.group))
+            ops.append(dist.P2POp(dist.isend, c, halo._peer(p), group=halo.group))
+    for p in halo.peers_in:
+        a, b = int(indptr[halo.recv_offsets[p]]), int(indptr[halo.recv_offsets[p] + halo.recv_counts[p]])
+        if b > a:
+            ops.append(dist.P2POp(dist.irecv, data[a:b], halo._peer(p), group=halo.group))
+            ops.append(dist.P2POp(dist.irecv, indices[a:b], halo._peer(p), group=halo.group))
+    HaloPlan._run(ops)
+    return data, indices, indptr
+
+
+def dist_spgemm(A, B):
+    """This rank's rows of C = A B for row-partitioned A (columns partitioned like B's rows) and B.
+    Returns ``(C_data, C_indices[global cols], C_indptr)``; the blocks of all ranks concatenate
+    to the single-device product.  Forward only (no autograd through the exchange)."""
+    halo = A.halo
+    h_data, h_indices, h_indptr = _fetch_rows(A, B)
+    n_ext = halo.n_local + halo.n_halo
+    ext_data = torch.cat((B.data.detach(), h_data))
+    ext_indices = torch.cat((B.global_indices, h_indices))
+    ext_indptr = torch.cat((B.indptr, h_indptr[1:] + B.indptr[-1]))
+    return A.ops.spgemm_forward(A.n_rows, n_ext, A.data.detach(), A.indices, A.indptr,
+                                n_ext, B.global_shape[1], ext_data, ext_indices, ext_indptr)
+
+
+def bench_steps(n, rank, world, dev, ops):
+    """Benchmark closures for bench.py at world > 1: every rank owns one n^3 slab (z-planes
+    rank*n .. (rank+1)*n) of the 7-point Laplacian on an n x n x (n*world) grid."""
+    from . import workloads as W
+    rows_per = n ** 3
+    bounds = [rows_per * r for r in range(world + 1)]
+    d, i, p, _ = W.poisson3d_7pt(n, torch.float64, nz=n * world, row_range=(bounds[rank], bounds[rank + 1]))
+    A = DistSparseCSR(d.to(dev), i.to(dev), p.to(dev), (rows_per * world, rows_per * world), bounds, ops=ops)
+    x_h = W.randn(rows_per, 100 + rank, torch.float64)
+    g_h = W.randn(rows_per, 200 + rank, torch.float64)
+    x, g = x_h.to(dev), g_h.to(dev)
+    A.requires_grad = True
+
+    def step_dev():
+        xg = x.detach().requires_grad_(True)
+        A.data.grad = None
+        y = A @ xg
+        y.backward(g)
+
+    x_pin, g_pin = x_h.pin_memory(), g_h.pin_memory()
+    y_pin = torch.empty(rows_per, dtype=torch.float64).pin_memory()
+    gx_pin = torch.empty(rows_per, dtype=torch.float64).pin_memory()
+    gA_pin = torch.empty(d.numel(), dtype=torch.float64).pin_memory()
+
+    def step_e2e():
+        xd = x_pin.to(dev, non_blocking=True).requires_grad_(True)
+        gd = g_pin.to(dev, non_blocking=True)
+        A.data.grad = None
+        yd = A @ xd
+        yd.backward(gd)
+        y_pin.copy_(yd.detach(), non_blocking=True)
+        gx_pin.copy_(xd.grad, non_blocking=True)
+        gA_pin.copy_(A.data.grad, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    n_ext = A.halo.n_local + A.halo.n_halo
+    info = {"nnz": int(d.numel()), "rows": rows_per, "cols": n_ext, "index_bytes": 4,
+            "launches_per_step": 3 + len(A.halo.peers_out),     # forward, grad_A pass, grad_x pass, one pack per peer
+            "h2d_bytes": 2 * rows_per * 8, "d2h_bytes": (2 * rows_per + int(d.numel())) * 8, "roofline": None}
+    return step_dev, step_e2e, info

@@ -16,17 +16,22 @@ def _pack(data, indices, indptr, shape, dtype):
             (int(shape[0]), int(shape[1])))
 
 
-def _stencil(dims, offsets, diag_val, off_val, dtype, lower_only=False):
+def _stencil(dims, offsets, diag_val, off_val, dtype, lower_only=False, row_range=None):
     """Dirichlet stencil on a regular grid in natural (row-major) ordering.
 
-    dims    : grid extents, slowest index first
-    offsets : list of index-offset tuples, excluding the centre
+    dims      : grid extents, slowest index first
+    offsets   : list of index-offset tuples, excluding the centre
+    row_range : (lo, hi) builds only rows lo..hi-1 (columns stay global); the returned shape is
+                (hi - lo, number of grid points)
     """
     dims = tuple(int(d) for d in dims)
-    n = int(np.prod(dims))
-    coords = np.unravel_index(np.arange(n, dtype=np.int64), dims)
+    ntot = int(np.prod(dims))
+    lo, hi = (0, ntot) if row_range is None else (int(row_range[0]), int(row_range[1]))
+    ids = np.arange(lo, hi, dtype=np.int64)
+    n = hi - lo
+    coords = np.unravel_index(ids, dims)
     strides = [int(np.prod(dims[k + 1:])) for k in range(len(dims))]
-    cols = [np.arange(n, dtype=np.int64)]
+    cols = [ids]
     vals = [np.full(n, diag_val, dtype=np.float64)]
     valid = [np.ones(n, dtype=bool)]
     for off in offsets:
@@ -38,7 +43,7 @@ def _stencil(dims, offsets, diag_val, off_val, dtype, lower_only=False):
             delta += o * strides[k]
         if lower_only and delta > 0:
             continue
-        cols.append(np.arange(n, dtype=np.int64) + delta)
+        cols.append(ids + delta)
         vals.append(np.full(n, off_val, dtype=np.float64))
         valid.append(ok)
     cols = np.stack(cols, axis=1)
@@ -51,7 +56,7 @@ def _stencil(dims, offsets, diag_val, off_val, dtype, lower_only=False):
     counts = valid.sum(axis=1)
     indptr = np.zeros(n + 1, dtype=np.int64)
     np.cumsum(counts, out=indptr[1:])
-    return _pack(vals[valid], cols[valid], indptr, (n, n), dtype)
+    return _pack(vals[valid], cols[valid], indptr, (n, ntot), dtype)
 
 
 def poisson2d_5pt(n, dtype=torch.float32):
@@ -59,10 +64,11 @@ def poisson2d_5pt(n, dtype=torch.float32):
     return _stencil((n, n), [(-1, 0), (0, -1), (0, 1), (1, 0)], 4.0, -1.0, dtype)
 
 
-def poisson3d_7pt(n, dtype=torch.float64):
-    """7-point Laplacian on an n^3 grid: 6 on the diagonal, -1 off; nnz = 7n^3 - 6n^2."""
+def poisson3d_7pt(n, dtype=torch.float64, nz=None, row_range=None):
+    """7-point Laplacian on an nz x n x n grid (nz = n by default): 6 on the diagonal, -1 off;
+    nnz = 7n^3 - 6n^2 for the cube.  ``row_range`` builds a block of rows only (global columns)."""
     offs = [(-1, 0, 0), (0, -1, 0), (0, 0, -1), (0, 0, 1), (0, 1, 0), (1, 0, 0)]
-    return _stencil((n, n, n), offs, 6.0, -1.0, dtype)
+    return _stencil((n if nz is None else nz, n, n), offs, 6.0, -1.0, dtype, row_range=row_range)
 
 
 def poisson2d_9pt_lower(n, dtype=torch.float64):

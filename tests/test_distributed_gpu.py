@@ -1,0 +1,58 @@
+"""Two NCCL ranks on two GPUs (skipped when fewer are visible): partitioned SpMV forward/backward
+with the CUDA kernels as local compute must equal the single-partition CPU oracle."""
+import os
+import sys
+import tempfile
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, init_file):
+    for p in (ROOT, os.path.join(ROOT, "oracle")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    import csr_oracle as oracle
+    from numml_b200 import distributed as nd, workloads as W
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method="file://" + init_file, rank=rank, world_size=world, device_id=dev)
+    try:
+        d, i, p, (m, n) = W.poisson3d_7pt(12, torch.float64, nz=12 * world)
+        bounds = nd.partition_rows(m, world)
+        lo, hi = bounds[rank], bounds[rank + 1]
+        sl = slice(int(p[lo]), int(p[hi]))
+        A = nd.DistSparseCSR(d[sl].to(dev), i[sl].to(dev), (p[lo:hi + 1] - p[lo]).to(dev), (m, n), bounds)
+        x, g = W.randn(n, 1, torch.float64), W.randn(m, 2, torch.float64)
+        y_ref = oracle.spgemv_forward(m, n, d, i, p, x)
+        gA_ref, gx_ref = oracle.spgemv_backward(g, m, n, d, i, p, x)
+        A.requires_grad = True
+        xl = x[lo:hi].to(dev).requires_grad_(True)
+        y = A @ xl
+        y.backward(g[lo:hi].to(dev))
+        assert torch.equal(y.detach().cpu(), y_ref[lo:hi])
+        assert torch.equal(A.data.grad.cpu(), gA_ref[sl])
+        assert torch.allclose(xl.grad.cpu(), gx_ref[lo:hi], rtol=1e-13, atol=1e-13)
+        Cd, Ci, Cp = A @ A
+        C_ref = oracle.spgemm_forward(m, n, d, i, p, m, n, d, i, p)
+        assert torch.equal(Cp.cpu(), C_ref[2][lo:hi + 1] - C_ref[2][lo])
+        assert torch.equal(Ci.cpu(), C_ref[1][int(C_ref[2][lo]):int(C_ref[2][hi])])
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_spmv_matches_oracle():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import csr_oracle
+    csr_oracle.build()
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_worker, args=(2, os.path.join(tmp, "rendezvous")), nprocs=2, join=True)
