@@ -245,6 +245,34 @@ NB200_API int nb200_masked_outer(int64_t rows, int64_t nnz, int64_t nrhs, const 
                                  const void* a, const void* b, double alpha, void* out,
                                  int dtype, int itype, nb200_stream stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Allocation-free float32 triangular solve.  No counterpart in the reference.
+ *
+ * Same computation and same results as nb200_sptrsv_solve with dtype NB200_F32, for callers that
+ * have no device memory to lend: a plugin embedded in a runtime that owns the device-memory pool
+ * and forbids allocation behind its back, or a latency-bound loop that must never reach cudaMalloc
+ * (which synchronises the device and can fail on a fragmented heap).  The n*nrhs doubles of working
+ * memory that the substitution needs live in a fixed 8 MiB array inside the library image (held by
+ * every GPU that loads the library, until the process exits) instead of a caller-provided `x_double`.
+ * The caller still passes every input and output, including the `status` word.
+ *
+ *   - n * nrhs may not exceed nb200_sptrsv_solve_f32_noalloc_capacity() (1,048,576); a larger
+ *     problem returns NB200_ERR_TOO_LARGE and launches nothing.
+ *   - The first call on a device looks up the device address of the array (with that device
+ *     current) and caches it; make that first call before any stream capture begins.
+ *   - All calls on a device share the one array.  It keeps the previous call's contents and is
+ *     re-marked "unsolved" at the start of every call, so sequential calls are independent; two
+ *     calls whose kernels overlap on the GPU (different streams, or different host threads) race on
+ *     it and give undefined results.
+ *   - The function calls no cudaMalloc / cudaFree and no allocating library routine.
+ * ------------------------------------------------------------------------------------------- */
+NB200_API int64_t nb200_sptrsv_solve_f32_noalloc_capacity(void);
+NB200_API int nb200_sptrsv_solve_f32_noalloc(int64_t n, int64_t nnz, int64_t nrhs,
+                                             const float* data, const void* indices, const void* indptr,
+                                             const void* perm, const int32_t* order, int lower, int unit,
+                                             const float* b, float* x, int32_t* status,
+                                             int64_t wait_budget_cycles, int itype, nb200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -21,6 +21,7 @@
 // wrong side of the diagonal, stored diagonal ignored with `unit`.  Results are bit-identical to
 // the reference CPU loop.
 #include "primitives.cuh"
+#include <mutex>
 
 namespace nb200 {
 
@@ -341,4 +342,53 @@ extern "C" int nb200_masked_outer(int64_t rows, int64_t nnz, int64_t nrhs, const
         (masked_outer_kernel<T, I><<<flat_grid(nnz), 256, 0, as_stream(stream)>>>(
              rows, nnz, nrhs, (const I*)indices, (const I*)indptr, (const T*)a, (const T*)b, (T)alpha, (T*)out),
          launch_status()));
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free float32 solve
+// ---------------------------------------------------------------------------------------------
+// A float32 solve substitutes in double, so it needs n*nrhs doubles of working memory besides its
+// inputs and outputs.  nb200_sptrsv_solve takes that array from the caller.  The variant below is
+// for hosts that cannot hand one over: a plugin living inside another runtime that owns the whole
+// device-memory pool and forbids further allocation, or a control loop that must not reach
+// cudaMalloc because it synchronises the device and can fail once memory is fragmented.  The
+// working array is a fixed region inside the library image instead; every GPU that loads the
+// library carries these 8 MiB until the process exits.
+constexpr int64_t kNoAllocSolveWords = 1 << 20;                       // doubles: n * nrhs may not exceed this
+static __device__ __align__(256) double g_noalloc_solve_words[kNoAllocSolveWords];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel could
+// use: the device address is looked up once per device, with that device current, and cached.
+static int noalloc_solve_words(double** out) {
+    static std::mutex mu;
+    static double* cached[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NB200_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_noalloc_solve_words) != cudaSuccess || p == nullptr) return NB200_ERR_CUDA;
+        cached[dev] = static_cast<double*>(p);
+    }
+    *out = cached[dev];
+    return NB200_OK;
+}
+
+extern "C" int64_t nb200_sptrsv_solve_f32_noalloc_capacity(void) { return kNoAllocSolveWords; }
+
+extern "C" int nb200_sptrsv_solve_f32_noalloc(int64_t n, int64_t nnz, int64_t nrhs,
+                                              const float* data, const void* indices, const void* indptr,
+                                              const void* perm, const int32_t* order, int lower, int unit,
+                                              const float* b, float* x, int32_t* status,
+                                              int64_t wait_budget_cycles, int itype, nb200_stream stream) {
+    if (n < 0 || nnz < 0 || nrhs < 0) return NB200_ERR_BAD_ARG;
+    if (n > 0 && nrhs > 0 && (n > kNoAllocSolveWords || nrhs > kNoAllocSolveWords / n)) return NB200_ERR_TOO_LARGE;
+    double* words = nullptr;
+    const int rc = noalloc_solve_words(&words);
+    if (rc != NB200_OK) return rc;
+    // nb200_sptrsv_solve refills the working array with the "not solved yet" marker on every call,
+    // so whatever the previous call left in the shared region is never read.
+    return nb200_sptrsv_solve(n, nnz, nrhs, data, indices, indptr, perm, order, lower, unit, b, x, words, status,
+                              wait_budget_cycles, NB200_F32, itype, stream);
 }
