@@ -189,6 +189,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--grid", type=int, default=128, help="grid extent n (the workload is n^3 rows per GPU)")
     ap.add_argument("--backward", default=None, choices=["transpose", "atomic"])
+    ap.add_argument("--spmv-kernel", default=None, choices=["auto", "stream"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -214,6 +215,8 @@ def main():
     from numml_b200 import numml_torch_cpp as ops
     if args.backward:
         ops.spmv_backward_mode = args.backward
+    if args.spmv_kernel:
+        ops.spmv_kernel = args.spmv_kernel
 
     n = args.grid
     peak, peak_kind = load_peaks()
@@ -278,6 +281,8 @@ def run(args, rank, world, dev, dist, n, peak, peak_kind):
     ms_e2e = timed(step_e2e, max(3, min(K, 20)), 3)
     e2e_steps = max(3, min(K, 20))
 
+    if info.get("status_word") is not None and int(info["status_word"].item()) != 0:
+        raise SystemExit("a bounded device-side wait ran out during the benchmark; results are invalid")
     value = bytes_per_step * K / (ms_dev * 1e-3) / 1e9
     e2e_value = bytes_per_step * e2e_steps / (ms_e2e * 1e-3) / 1e9
 
@@ -286,7 +291,7 @@ def run(args, rank, world, dev, dist, n, peak, peak_kind):
         "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f64", "data": "synthetic",
         "config": {"workload": f"poisson3d_7pt_{n}^3_per_gpu_fp64_spmv_fwd_bwd", "rows_per_gpu": m, "nnz_per_gpu": nnz,
-                   "index_bytes": w, "backward": ops.spmv_backward_mode,
+                   "index_bytes": w, "backward": ops.spmv_backward_mode, "kernels": info.get("kernels"),
                    "partition": "z-slabs, one halo plane per neighbour" if world > 1 else "single GPU",
                    "l2": "working set per step (>= 350 MB) is larger than the 126 MB L2; no explicit flush"},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / e2e_steps,
@@ -318,12 +323,20 @@ def single_gpu_steps(A, x_h, g_h, dev, ops, _plan, _cabi, P, stream):
     grad_x = torch.empty(k, dtype=torch.float64, device=dev)
     data = A.data
 
+    pipelined = ops.spmv_kernel == "auto"
+    br = plan.spmv_block_rows() if pipelined else 0
+    tbr = plan.spmv_block_rows(transposed=True) if (pipelined and transposed) else 0
+    sym = int(bool(br) and transposed and plan.pattern_symmetric())
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
     def fwd():
-        _cabi.call("nb200_spgemv_forward", m, k, nnz, P(data), P(idx), P(ptr), None, P(x), P(y), _cabi.F64, itype, stream())
+        _cabi.call("nb200_spgemv_forward", m, k, nnz, P(data), P(idx), P(ptr), None, P(x), P(y), br, P(status),
+                   _cabi.F64, itype, stream())
 
     def bwd():
         _cabi.call("nb200_spgemv_backward", m, k, nnz, P(data), P(idx), P(ptr), P(x), P(g),
-                   P(t_indptr), P(t_indices), P(t_perm), P(grad_A), P(grad_x), _cabi.F64, itype, stream())
+                   P(t_indptr), P(t_indices), P(t_perm), P(grad_A), P(grad_x), br, tbr, sym, P(status),
+                   _cabi.F64, itype, stream())
 
     def step_dev():
         fwd()
@@ -362,7 +375,8 @@ def single_gpu_steps(A, x_h, g_h, dev, ops, _plan, _cabi, P, stream):
     def roofline(peak, peak_kind):
         fwd_b, bwd_b = algorithmic_bytes(m, k, nnz, 8, w)
         t_f, t_b = kernel_us(fwd), kernel_us(bwd)
-        dominant = "spmv_backward (grad_A stream pass + grad_x pass)" if t_b >= t_f else "spmv_forward"
+        bwd_name = "spmv_backward (one fused pass, symmetric pattern)" if sym else "spmv_backward (grad_A pass + grad_x pass)"
+        dominant = bwd_name if t_b >= t_f else "spmv_forward"
         bytes_, t = (bwd_b, t_b) if t_b >= t_f else (fwd_b, t_f)
         ach = bytes_ / (t * 1e-6) / 1e9
         return {"bound": "hbm", "kernel": dominant, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
@@ -371,8 +385,9 @@ def single_gpu_steps(A, x_h, g_h, dev, ops, _plan, _cabi, P, stream):
                 "forward": {"us": t_f, "GBps": fwd_b / (t_f * 1e-6) / 1e9, "frac": fwd_b / (t_f * 1e-6) / 1e9 / peak},
                 "backward": {"us": t_b, "GBps": bwd_b / (t_b * 1e-6) / 1e9, "frac": bwd_b / (t_b * 1e-6) / 1e9 / peak}}
 
-    info = {"nnz": nnz, "rows": m, "cols": k, "index_bytes": w,
-            "launches_per_step": 3 if transposed else 2,
+    info = {"nnz": nnz, "rows": m, "cols": k, "index_bytes": w, "kernels": "tma-pipelined" if br else "register-staged",
+            "status_word": status,
+            "launches_per_step": (2 if sym else 3) if transposed else 2,
             "h2d_bytes": (m + k) * 8, "d2h_bytes": (m + k + nnz) * 8, "roofline": roofline}
     return step_dev, step_e2e, info
 

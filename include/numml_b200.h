@@ -61,11 +61,22 @@ NB200_API const char* nb200_status_string(int status);
  * the row-streaming kernel (mean row length <= 24) the result is bit-identical to the reference
  * CPU loop.  `perm` (itype, may be NULL): when given, entry k uses data[perm[k]] -- this is how
  * a cached transposed structure is applied to the current values (y = A^T g).
+ * `block_rows` selects the kernel: 0 = register-staged streaming (any matrix); R in 1..256 = the
+ * persistent TMA-pipelined kernel, valid only if every block of R consecutive rows holds at most
+ * nb200_spmv_pipeline_tile() entries (see nb200_csr_block_profile); the result is the same.
+ * `status` (device word, may be NULL) receives NB200_ERR_WAIT_BUDGET if a bounded wait of the
+ * pipelined kernel ever runs out.
  * ------------------------------------------------------------------------------------------- */
 NB200_API int nb200_spgemv_forward(int64_t rows, int64_t cols, int64_t nnz,
                          const void* data, const void* indices, const void* indptr,
                          const void* perm, const void* x, void* y,
+                         int block_rows, int32_t* status,
                          int dtype, int itype, nb200_stream stream);
+
+/* Largest number of entries in any block of R consecutive rows, for R = 256, 128, 64, 32, written to
+ * the four int64 device words out4[0..3]; and the entry capacity of one pipeline stage. */
+NB200_API int nb200_csr_block_profile(int64_t rows, const void* indptr, int itype, int64_t* out4, nb200_stream stream);
+NB200_API int nb200_spmv_pipeline_tile(void);
 
 /* ---------------------------------------------------------------------------------------------
  * SpMV backward.                  Replaces spgemv_backward (reference cpp/sparse_csr.hpp:38-42,
@@ -76,13 +87,18 @@ NB200_API int nb200_spgemv_forward(int64_t rows, int64_t cols, int64_t nnz,
  * t_perm[nnz] = position in A of each entry of A^T; see nb200_csr_transpose_structure) grad_x is
  * a gather over A^T: atomic-free, deterministic and bit-identical to the reference.  With the
  * three t_* pointers NULL grad_x is zeroed and accumulated with floating-point atomics in one
- * fused pass over A (order of additions not fixed).
+ * fused pass over A (order of additions not fixed).  `block_rows` / `t_block_rows` choose the
+ * kernel for the pass over A / over A^T as in nb200_spgemv_forward (0 = streaming kernels).
+ * `pattern_symmetric` != 0 asserts that the pattern equals its transpose (t_indptr == indptr,
+ * t_indices == indices); with block_rows > 0 both gradients then come from ONE pipelined pass
+ * that reads indices and t_perm once (same results, bit for bit).
  * ------------------------------------------------------------------------------------------- */
 NB200_API int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
                           const void* data, const void* indices, const void* indptr,
                           const void* x, const void* g,
                           const void* t_indptr, const void* t_indices, const void* t_perm,
                           void* grad_A, void* grad_x,
+                          int block_rows, int t_block_rows, int pattern_symmetric, int32_t* status,
                           int dtype, int itype, nb200_stream stream);
 
 /* ---------------------------------------------------------------------------------------------

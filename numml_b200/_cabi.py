@@ -18,8 +18,11 @@ I32, I64 = 0, 1
 SIGNATURES = {
     "nb200_version": (_int, []),
     "nb200_status_string": (_c.c_char_p, [_int]),
-    "nb200_spgemv_forward": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
-    "nb200_spgemv_backward": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
+    "nb200_spgemv_forward": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp, _int, _int, _vp]),
+    "nb200_spgemv_backward": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _int,
+                                     _vp, _int, _int, _vp]),
+    "nb200_csr_block_profile": (_int, [_i64, _vp, _int, _vp, _vp]),
+    "nb200_spmv_pipeline_tile": (_int, []),
     "nb200_csr_transpose_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "nb200_csr_transpose_structure": (_int, [_i64, _i64, _i64, _vp, _vp, _int, _vp, _vp, _vp, _int, _vp, _sz, _vp]),
     "nb200_gather": (_int, [_i64, _vp, _vp, _vp, _int, _int, _vp]),

@@ -68,6 +68,44 @@ class PatternPlan:
         return self._t
 
 
+    def pattern_symmetric(self):
+        """True if the sparsity pattern equals its transpose (stencils, undirected graphs)."""
+        if "symmetric" not in self.extra:
+            ok = self.rows == self.cols
+            if ok:
+                idx, ptr, _ = self.csr()
+                t_indptr, t_indices, _, _ = self.transpose()
+                ok = bool(torch.equal(t_indptr, ptr)) and bool(torch.equal(t_indices, idx))
+            self.extra["symmetric"] = ok
+        return self.extra["symmetric"]
+
+    # -- kernel choice for SpMV ---------------------------------------------------------------------
+    def spmv_block_rows(self, transposed=False):
+        """Rows per block for the TMA-pipelined SpMV kernels over this pattern (or over its
+        transpose), or 0 when the pattern is too irregular for them: the largest R in (256, 128)
+        such that every block of R consecutive rows fits one pipeline stage."""
+        key = ("spmv_block_rows", bool(transposed))
+        if key not in self.extra:
+            if transposed:
+                ptr, _, _, itype = self.transpose()
+                rows = self.cols
+            else:
+                _, ptr, itype = self.csr()
+                rows = self.rows
+            dev = self.indices.device
+            with torch.cuda.device(dev):
+                out = torch.empty(4, dtype=torch.int64, device=dev)
+                _cabi.call("nb200_csr_block_profile", rows, _ptr(ptr), itype, _ptr(out), _stream())
+                maxima = out.cpu().tolist()
+            tile = _cabi.lib().nb200_spmv_pipeline_tile()
+            choice = 0
+            for c, R in enumerate((256, 128)):
+                if maxima[c] <= tile:
+                    choice = R
+                    break
+            self.extra[key] = choice if self.nnz > 0 else 0
+        return self.extra[key]
+
     # -- triangular-solve schedules ----------------------------------------------------------------
     def sptrsv_order(self, lower, transposed=False):
         """(order, nlevels) for solving with this pattern (``transposed=False``) or with its

@@ -14,6 +14,7 @@
 // pass with floating-point atomics, or computed by the forward kernel on a cached transposed
 // structure whose values are gathered through a permutation (atomic-free, deterministic).
 #include "common.cuh"
+#include "spmv_pipe.cuh"
 
 namespace nb200 {
 
@@ -252,8 +253,10 @@ static inline int stream_rows_per_cta(int64_t rows, int64_t nnz) {
 
 template <typename T, typename I>
 int spmv_forward_launch(int64_t rows, int64_t nnz, const T* data, const I* indices, const I* indptr,
-                        const I* perm, const T* x, T* y, cudaStream_t st) {
+                        const I* perm, const T* x, T* y, int block_rows, int32_t* status, cudaStream_t st) {
     if (rows == 0) return NB200_OK;
+    if (block_rows > 0 && nnz > 0)
+        return spmv_pipe_forward<T, I>(rows, nnz, block_rows, data, indices, indptr, perm, x, y, status, st);
     const double mean = (double)nnz / (double)rows;
     if (mean <= kStreamMaxMeanRow) {
         const int rpc = stream_rows_per_cta(rows, nnz);
@@ -279,14 +282,21 @@ int spmv_forward_launch(int64_t rows, int64_t nnz, const T* data, const I* indic
 template <typename T, typename I>
 int spmv_backward_launch(int64_t rows, int64_t cols, int64_t nnz, const T* data, const I* indices,
                          const I* indptr, const T* x, const T* g, const I* t_indptr,
-                         const I* t_indices, const I* t_perm, T* grad_A, T* grad_x, cudaStream_t st) {
+                         const I* t_indices, const I* t_perm, T* grad_A, T* grad_x, int block_rows, int t_block_rows,
+                         bool pattern_symmetric, int32_t* status, cudaStream_t st) {
     const bool atomic = (t_indptr == nullptr);
+    if (!atomic && pattern_symmetric && block_rows > 0 && rows == cols && nnz > 0)
+        return spmv_pipe_backward_sym<T, I>(rows, nnz, block_rows, data, indices, indptr, t_perm, x, g, grad_A, grad_x,
+                                            status, st);
     if (atomic && cols > 0) {
         if (cudaMemsetAsync(grad_x, 0, sizeof(T) * (size_t)cols, st) != cudaSuccess) return NB200_ERR_CUDA;
     }
     if (rows > 0 && nnz > 0) {
         const double mean = (double)nnz / (double)rows;
-        if (mean <= kStreamMaxMeanRow) {
+        if (!atomic && block_rows > 0) {
+            int rc = spmv_pipe_grad_A<T, I>(rows, nnz, block_rows, indices, indptr, x, g, grad_A, status, st);
+            if (rc != NB200_OK) return rc;
+        } else if (mean <= kStreamMaxMeanRow) {
             const int rpc = stream_rows_per_cta(rows, nnz);
             const int64_t grid = ceil_div(rows, (int64_t)rpc);
             if (grid > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
@@ -309,7 +319,7 @@ int spmv_backward_launch(int64_t rows, int64_t cols, int64_t nnz, const T* data,
     }
     if (!atomic) {
         // grad_x = A^T g through the transposed structure: rows of A^T are the columns of A.
-        return spmv_forward_launch<T, I>(cols, nnz, data, t_indices, t_indptr, t_perm, g, grad_x, st);
+        return spmv_forward_launch<T, I>(cols, nnz, data, t_indices, t_indptr, t_perm, g, grad_x, t_block_rows, status, st);
     }
     return NB200_OK;
 }
@@ -321,15 +331,17 @@ using namespace nb200;
 extern "C" int nb200_spgemv_forward(int64_t rows, int64_t cols, int64_t nnz,
                                     const void* data, const void* indices, const void* indptr,
                                     const void* perm, const void* x, void* y,
+                                    int block_rows, int32_t* status,
                                     int dtype, int itype, nb200_stream stream) {
     if (rows < 0 || cols < 0 || nnz < 0) return NB200_ERR_BAD_ARG;
     if (rows == 0) return NB200_OK;
+    if (block_rows < 0 || block_rows > 256) return NB200_ERR_BAD_ARG;
     if (!indptr || !y || (nnz > 0 && (!data || !indices || !x))) return NB200_ERR_BAD_ARG;
     if (!aligned16(data) || !aligned16(indices) || !aligned16(perm)) return NB200_ERR_ALIGN;
     if (itype == NB200_I32 && nnz > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
     return NB200_DISPATCH(dtype, itype,
         (spmv_forward_launch<T, I>(rows, nnz, (const T*)data, (const I*)indices, (const I*)indptr,
-                                   (const I*)perm, (const T*)x, (T*)y, as_stream(stream))));
+                                   (const I*)perm, (const T*)x, (T*)y, block_rows, status, as_stream(stream))));
 }
 
 extern "C" int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
@@ -337,16 +349,58 @@ extern "C" int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
                                      const void* x, const void* g,
                                      const void* t_indptr, const void* t_indices, const void* t_perm,
                                      void* grad_A, void* grad_x,
+                                     int block_rows, int t_block_rows, int pattern_symmetric, int32_t* status,
                                      int dtype, int itype, nb200_stream stream) {
     if (rows < 0 || cols < 0 || nnz < 0) return NB200_ERR_BAD_ARG;
     if (!indptr || (cols > 0 && !grad_x) || (nnz > 0 && (!data || !indices || !x || !g || !grad_A)))
         return NB200_ERR_BAD_ARG;
     if (t_indptr != nullptr && nnz > 0 && (!t_indices || !t_perm)) return NB200_ERR_BAD_ARG;
+    if (block_rows < 0 || block_rows > 256 || t_block_rows < 0 || t_block_rows > 256) return NB200_ERR_BAD_ARG;
     if (!aligned16(data) || !aligned16(indices) || !aligned16(grad_A) || !aligned16(t_indices) || !aligned16(t_perm))
         return NB200_ERR_ALIGN;
     if (itype == NB200_I32 && nnz > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
     return NB200_DISPATCH(dtype, itype,
         (spmv_backward_launch<T, I>(rows, cols, nnz, (const T*)data, (const I*)indices, (const I*)indptr,
                                     (const T*)x, (const T*)g, (const I*)t_indptr, (const I*)t_indices,
-                                    (const I*)t_perm, (T*)grad_A, (T*)grad_x, as_stream(stream))));
+                                    (const I*)t_perm, (T*)grad_A, (T*)grad_x, block_rows, t_block_rows,
+                                    pattern_symmetric != 0, status, as_stream(stream))));
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Block profile: the largest number of entries in any block of R consecutive rows, for
+// R = 256, 128, 64, 32.  The host picks the largest R whose maximum fits one pipeline stage.
+// ---------------------------------------------------------------------------------------------
+namespace nb200 {
+template <typename I>
+__global__ void csr_block_profile_kernel(int64_t rows, const I* __restrict__ indptr, unsigned long long* __restrict__ out) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t gtid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int64_t R = 256 >> c;
+        const int64_t blocks = ceil_div(rows, R);
+        long long best = 0;
+        for (int64_t b = gtid; b < blocks; b += stride) {
+            const int64_t r1 = min((b + 1) * R, rows);
+            best = max(best, (long long)indptr[r1] - (long long)indptr[b * R]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+        if ((threadIdx.x & 31) == 0 && best > 0) atomicMax(out + c, (unsigned long long)best);
+    }
+}
+}  // namespace nb200
+
+extern "C" int nb200_spmv_pipeline_tile(void) { return kSpmvPipeTile; }
+
+extern "C" int nb200_csr_block_profile(int64_t rows, const void* indptr, int itype, int64_t* out4, nb200_stream stream) {
+    if (rows < 0 || !out4 || (rows > 0 && !indptr)) return NB200_ERR_BAD_ARG;
+    cudaStream_t st = as_stream(stream);
+    if (cudaMemsetAsync(out4, 0, 4 * sizeof(int64_t), st) != cudaSuccess) return NB200_ERR_CUDA;
+    if (rows == 0) return NB200_OK;
+    const int64_t want = ceil_div(ceil_div(rows, (int64_t)32), (int64_t)256);
+    const unsigned grid = (unsigned)(want > (int64_t)kSMs * 8 ? (int64_t)kSMs * 8 : want);
+    return NB200_DISPATCH_I(itype,
+        (csr_block_profile_kernel<I><<<grid, 256, 0, st>>>(rows, (const I*)indptr, (unsigned long long*)out4), launch_status()));
 }

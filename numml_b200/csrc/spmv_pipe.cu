@@ -1,0 +1,373 @@
+// Persistent, TMA-pipelined SpMV kernels for matrices whose rows are short and regular (the
+// stencil case): every block of `block_rows` consecutive rows holds at most kPipeTile nonzeros.
+//
+// One CTA per SM slot walks its share of the row blocks.  A producer warp runs ahead: for each
+// block it reads the block's nonzero range from indptr and issues bulk asynchronous copies
+// (cp.async.bulk, completion counted on an mbarrier) of the block's index and value streams into
+// one of kPipeStages shared-memory stages.  Eight consumer warps wait for a stage; then every
+// consumer thread owns one row of the block: it reads the row's entries from the stage, gathers x
+// through L1/L2 and accumulates in storage order (unfused multiply and add: bit-identical to a
+// sequential CPU loop).  Thread-per-row gathers are what makes banded matrices cheap: lanes of a
+// warp read x at consecutive addresses for each entry position, a few cache lines per
+// instruction instead of one per lane.  The DRAM stream never stops while a block is being
+// consumed, which is what the register-staged kernel in spmv.cu cannot do.
+//
+// Three modes share the pipeline:
+//   kForward       stage = values + column indices            y[r]      = sum_k data[k] x[col[k]]
+//   kForwardPerm   stage = column indices + permutation        y[r]      = sum_k data[perm[k]] x[col[k]]
+//   kGradA         stage = column indices                      grad_A[k] = g[row(k)] x[col[k]]
+//   kBackwardSym   stage = column indices + permutation        both gradients in one pass, for patterns that
+//                                                              equal their transpose (stencils, undirected graphs)
+//
+// Every wait on an mbarrier is a bounded try_wait loop; if the bound is hit the CTA records
+// NB200_ERR_WAIT_BUDGET in the status word (when one is given) and leaves its block loop.
+#include "spmv_pipe.cuh"
+
+namespace nb200 {
+
+constexpr int kPipeTile = kSpmvPipeTile;   // nonzeros per stage
+constexpr int kPipeConsumers = 256;   // consumer threads (8 warps); one more warp produces
+constexpr int kPipeThreads = kPipeConsumers + 32;
+constexpr unsigned kPipeSpinLimit = 1u << 24;
+
+enum PipeMode { kForward = 0, kForwardPerm = 1, kGradA = 2, kBackwardSym = 3 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}"
+                 :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false if the bound was hit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (unsigned spins = 0; spins < kPipeSpinLimit; ++spins) {
+        unsigned done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+// Bulk copy global -> shared, completion signalled on `bar`.  16-byte aligned, size % 16 == 0.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" :: "n"(kPipeConsumers) : "memory"); }
+
+template <typename T, typename I>
+struct PipeArgs {
+    int64_t rows, nnz, num_blocks;
+    int block_rows;
+    const T* data;       // values of A
+    const I* indices;    // column of each staged entry
+    const I* indptr;     // row pointers of the staged structure
+    const I* perm;       // kForwardPerm: position in `data` of each staged entry
+    const T* vec;        // gathered by column: x (forward, grad_A) or g (transposed pass)
+    const T* rowvec;     // kGradA / kBackwardSym: g, one factor per row
+    T* out;              // y [rows] or grad_A [nnz]
+    T* out2;             // kBackwardSym: grad_x [rows]
+    int32_t* status;     // may be null
+};
+
+template <typename T, typename I, int MODE, int S, bool DIRECT = false>
+struct PipeSmem {
+    static constexpr bool has_a = MODE != kGradA;
+    static constexpr bool a_is_perm = MODE == kForwardPerm || MODE == kBackwardSym;
+    static constexpr bool has_p = (MODE == kGradA || MODE == kBackwardSym) && !DIRECT;
+    static constexpr size_t a_bytes = has_a ? (a_is_perm ? sizeof(I) : sizeof(T)) * kPipeTile : 0;  // values | perm
+    static constexpr size_t b_bytes = sizeof(I) * kPipeTile;                                           // indices
+    static constexpr size_t p_bytes = has_p ? sizeof(T) * kPipeTile : 0;                               // grad_A staging
+    static constexpr size_t stage_bytes = a_bytes + b_bytes + p_bytes;
+    static constexpr size_t header_bytes = 128;
+    static constexpr size_t total = header_bytes + stage_bytes * S;
+};
+
+template <typename T>
+__device__ __forceinline__ void lds4(const T* p, T (&v)[4]);
+template <>
+__device__ __forceinline__ void lds4<float>(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <>
+__device__ __forceinline__ void lds4<double>(const double* p, double (&v)[4]) {
+    const double2 a = *reinterpret_cast<const double2*>(p), b = *reinterpret_cast<const double2*>(p + 2);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void lds4<int32_t>(const int32_t* p, int32_t (&v)[4]) {
+    const int4 t = *reinterpret_cast<const int4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <>
+__device__ __forceinline__ void lds4<int64_t>(const int64_t* p, int64_t (&v)[4]) {
+    const longlong2 a = *reinterpret_cast<const longlong2*>(p), b = *reinterpret_cast<const longlong2*>(p + 2);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <typename T>
+__device__ __forceinline__ void sts4(T* p, const T (&v)[4]);
+template <>
+__device__ __forceinline__ void sts4<float>(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <>
+__device__ __forceinline__ void sts4<double>(double* p, const double (&v)[4]) {
+    *reinterpret_cast<double2*>(p) = make_double2(v[0], v[1]);
+    *reinterpret_cast<double2*>(p + 2) = make_double2(v[2], v[3]);
+}
+
+template <typename T, typename I, int MODE, int S, int CH, int MINB, bool DIRECT>
+__global__ void __launch_bounds__(kPipeThreads, MINB)
+spmv_pipe_kernel(const PipeArgs<T, I> a) {
+    using L = PipeSmem<T, I, MODE, S, DIRECT>;
+    constexpr int kPipeStages = S;
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + kPipeStages;
+    auto stage_ptr = [&](int s) { return smem + L::header_bytes + (size_t)s * L::stage_bytes; };
+    // per stage: [A: values or perm (absent for kGradA)] [B: indices] [P: grad_A staging (kGradA only)]
+    auto stage_A = [&](int s) { return stage_ptr(s); };
+    auto stage_B = [&](int s) { return stage_ptr(s) + L::a_bytes; };
+    auto stage_P = [&](int s) { return stage_ptr(s) + L::a_bytes + L::b_bytes; };
+
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        for (int s = 0; s < kPipeStages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, kPipeConsumers / 32); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int64_t nnz_bulk_end = a.nnz & ~(int64_t)3;   // bulk copies never read past the arrays
+
+    if (tid >= kPipeConsumers) {
+        // ---------------------------------- producer warp ----------------------------------
+        if (tid != kPipeConsumers) return;
+        auto block_range = [&](int64_t blk, int64_t& begin_, int64_t& end_) {
+            begin_ = 0; end_ = 0;
+            if (blk < a.num_blocks) {
+                const int64_t q0 = blk * a.block_rows, q1 = min(q0 + (int64_t)a.block_rows, a.rows);
+                begin_ = (int64_t)a.indptr[q0];
+                end_ = (int64_t)a.indptr[q1];
+            }
+        };
+        int64_t it = 0, begin, end, begin_nxt, end_nxt;
+        block_range(blockIdx.x, begin, end);
+        for (int64_t b = blockIdx.x; b < a.num_blocks; b += gridDim.x, ++it, begin = begin_nxt, end = end_nxt) {
+            const int s = (int)(it % kPipeStages);
+            const unsigned ph = (unsigned)((it / kPipeStages) & 1);
+            block_range(b + gridDim.x, begin_nxt, end_nxt);   // in flight while this block's copies are issued
+            const int64_t base = begin & ~(int64_t)3;
+            int64_t stop = min((end + 3) & ~(int64_t)3, nnz_bulk_end);
+            int64_t count = stop > base ? stop - base : 0;
+            if (count > kPipeTile) count = kPipeTile;
+            if (!mbar_wait(empty + s, ph ^ 1u)) { if (a.status) atomicExch(a.status, (int)NB200_ERR_WAIT_BUDGET); return; }
+            if (count == 0) { mbar_arrive(full + s); continue; }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            const unsigned bytes_b = (unsigned)(count * sizeof(I));
+            if (MODE == kForward) {
+                const unsigned bytes_a = (unsigned)(count * sizeof(T));
+                mbar_arrive_expect_tx(full + s, bytes_a + bytes_b);
+                bulk_load(stage_A(s), a.data + base, bytes_a, full + s);
+                bulk_load(stage_B(s), a.indices + base, bytes_b, full + s);
+            } else if (MODE == kForwardPerm || MODE == kBackwardSym) {
+                mbar_arrive_expect_tx(full + s, 2 * bytes_b);
+                bulk_load(stage_A(s), a.perm + base, bytes_b, full + s);
+                bulk_load(stage_B(s), a.indices + base, bytes_b, full + s);
+            } else {
+                mbar_arrive_expect_tx(full + s, bytes_b);
+                bulk_load(stage_B(s), a.indices + base, bytes_b, full + s);
+            }
+        }
+        return;
+    }
+
+    // ------------------------------------ consumer warps ------------------------------------
+    // Per block each thread needs the block's nonzero range (same for all threads) and, if it owns
+    // a row of the block, that row's range (and g for kGradA).  They are fetched one block ahead so
+    // that their latency is hidden behind the current block's work.
+    struct BlockInfo { int64_t begin, end, s, e; T g; };
+    auto fetch = [&](int64_t blk) {
+        BlockInfo f{0, 0, 0, 0, (T)0};
+        if (blk < a.num_blocks) {
+            const int64_t r0 = blk * a.block_rows, r1 = min(r0 + (int64_t)a.block_rows, a.rows);
+            f.begin = (int64_t)a.indptr[r0];
+            f.end = (int64_t)a.indptr[r1];
+            const int64_t r = r0 + tid;
+            if (tid < a.block_rows && r < r1) {
+                f.s = (int64_t)a.indptr[r];
+                f.e = (int64_t)a.indptr[r + 1];
+                if (MODE == kGradA || MODE == kBackwardSym) f.g = a.rowvec[r];
+            }
+        }
+        return f;
+    };
+
+    int64_t it = 0;
+    BlockInfo cur = fetch(blockIdx.x);
+    for (int64_t b = blockIdx.x; b < a.num_blocks; b += gridDim.x, ++it) {
+        const int s = (int)(it % kPipeStages);
+        const unsigned ph = (unsigned)((it / kPipeStages) & 1);
+        const BlockInfo nxt = fetch(b + gridDim.x);
+
+        const int64_t r0 = b * a.block_rows, r1 = min(r0 + (int64_t)a.block_rows, a.rows);
+        const int64_t begin = cur.begin, end = cur.end;
+        const int64_t base = begin & ~(int64_t)3;
+        const int64_t bulk_stop = min(min((end + 3) & ~(int64_t)3, nnz_bulk_end), base + kPipeTile);
+        const bool owns_row = tid < a.block_rows && r0 + tid < r1;
+        const int64_t stage_end = min(bulk_stop, base + kPipeTile);   // entries below this are in the stage
+
+        if (!mbar_wait(full + s, ph)) {
+            if (a.status && tid == 0) atomicExch(a.status, (int)NB200_ERR_WAIT_BUDGET);
+            return;
+        }
+        const I* sidx = reinterpret_cast<const I*>(stage_B(s));
+        const T* sval = reinterpret_cast<const T*>(stage_A(s));     // kForward
+        const I* sperm = reinterpret_cast<const I*>(stage_A(s));    // kForwardPerm, kBackwardSym
+        T* sout = reinterpret_cast<T*>(stage_P(s));                 // kGradA, kBackwardSym
+
+        // ---- one thread per row: entries from the stage, x through L1/L2, storage order ----
+        if (owns_row) {
+            T acc = 0;
+            for (int64_t k0 = cur.s; k0 < cur.e; k0 += CH) {
+                const int n = (int)min((int64_t)CH, cur.e - k0);
+                I c[CH];
+                T v[CH], xv[CH];
+#pragma unroll
+                for (int j = 0; j < CH; ++j) {
+                    c[j] = 0; v[j] = 0;
+                    if (j < n) {
+                        const int64_t k = k0 + j;
+                        const bool staged = k < stage_end;
+                        c[j] = staged ? sidx[k - base] : a.indices[k];
+                        if (MODE == kForward) v[j] = staged ? sval[k - base] : a.data[k];
+                        if (MODE == kForwardPerm || MODE == kBackwardSym)
+                            v[j] = ldg(a.data + (staged ? sperm[k - base] : a.perm[k]));
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < CH; ++j) xv[j] = (j < n) ? ldg(a.vec + c[j]) : (T)0;
+                if (MODE == kBackwardSym) {
+                    // the pattern equals its transpose: row i of A^T has the same columns, so one pass
+                    // gives grad_A[k] = g_i x_c and grad_x[i] = sum_k A^T[i,c] g_c
+                    T gv[CH];
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) gv[j] = (j < n) ? ldg(a.rowvec + c[j]) : (T)0;
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) {
+                        if (j < n) {
+                            const int64_t k = k0 + j;
+                            const T o = mul_rn(cur.g, xv[j]);
+                            if (!DIRECT && k < base + kPipeTile) sout[k - base] = o; else a.out[k] = o;
+                            acc = add_rn(acc, mul_rn(gv[j], v[j]));
+                        }
+                    }
+                } else if (MODE == kGradA) {
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) {
+                        if (j < n) {
+                            const int64_t k = k0 + j;
+                            const T o = mul_rn(cur.g, xv[j]);
+                            if (k < base + kPipeTile) sout[k - base] = o; else a.out[k] = o;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < CH; ++j)
+                        if (j < n) acc = add_rn(acc, mul_rn(v[j], xv[j]));
+                }
+            }
+            if (MODE == kForward || MODE == kForwardPerm) a.out[r0 + tid] = acc;
+            if (MODE == kBackwardSym) a.out2[r0 + tid] = acc;
+        }
+        if ((MODE == kGradA || MODE == kBackwardSym) && !DIRECT) {
+            // ---- coalesced 128-bit stores of the block's grad_A entries ----
+            consumer_sync();
+            const int64_t lim = min(end, base + kPipeTile);
+#pragma unroll
+            for (int u = 0; u < kPipeTile / (kPipeConsumers * 4); ++u) {
+                const int off = (u * kPipeConsumers + tid) * 4;
+                const int64_t k = base + off;
+                if (k < lim) {
+                    if (k >= begin && k + 4 <= lim) {
+                        T o[4];
+                        lds4<T>(sout + off, o);
+                        store4_stream(a.out + k, o);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (k + j >= begin && k + j < lim) a.out[k + j] = sout[off + j];
+                    }
+                }
+            }
+        }
+        // release the stage: one arrival per consumer warp, after all of its lanes are done with it
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(empty + s);
+        cur = nxt;
+    }
+}
+
+template <typename T, typename I, int MODE, int S, int CH = 8, int MINB = 3, bool DIRECT = false>
+int spmv_pipe_launch(const PipeArgs<T, I>& args, cudaStream_t st) {
+    using L = PipeSmem<T, I, MODE, S, DIRECT>;
+    static bool configured = false;
+    auto kernel = spmv_pipe_kernel<T, I, MODE, S, CH, MINB, DIRECT>;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::total) != cudaSuccess)
+            return NB200_ERR_CUDA;
+        configured = true;
+    }
+    int per_sm = (int)((size_t)(227 * 1024) / (L::total + 1024));
+    if (per_sm > MINB) per_sm = MINB;
+    const int64_t want = (int64_t)kSMs * (per_sm < 1 ? 1 : per_sm);
+    const unsigned grid = (unsigned)(args.num_blocks < want ? args.num_blocks : want);
+    kernel<<<grid, kPipeThreads, L::total, st>>>(args);
+    return launch_status();
+}
+
+// Entry points used by spmv.cu
+template <typename T, typename I>
+int spmv_pipe_forward(int64_t rows, int64_t nnz, int block_rows, const T* data, const I* indices, const I* indptr,
+                      const I* perm, const T* x, T* y, int32_t* status, cudaStream_t st) {
+    PipeArgs<T, I> a{rows, nnz, ceil_div(rows, (int64_t)block_rows), block_rows, data, indices, indptr, perm, x, nullptr, y, nullptr, status};
+    return perm ? spmv_pipe_launch<T, I, kForwardPerm, 3>(a, st) : spmv_pipe_launch<T, I, kForward, 3>(a, st);
+}
+
+template <typename T, typename I>
+int spmv_pipe_grad_A(int64_t rows, int64_t nnz, int block_rows, const I* indices, const I* indptr, const T* x,
+                     const T* g, T* grad_A, int32_t* status, cudaStream_t st) {
+    PipeArgs<T, I> a{rows, nnz, ceil_div(rows, (int64_t)block_rows), block_rows, nullptr, indices, indptr, nullptr, x, g, grad_A, nullptr, status};
+    return spmv_pipe_launch<T, I, kGradA, 3>(a, st);
+}
+
+template <typename T, typename I>
+int spmv_pipe_backward_sym(int64_t rows, int64_t nnz, int block_rows, const T* data, const I* indices, const I* indptr,
+                           const I* perm, const T* x, const T* g, T* grad_A, T* grad_x, int32_t* status, cudaStream_t st) {
+    PipeArgs<T, I> a{rows, nnz, ceil_div(rows, (int64_t)block_rows), block_rows, data, indices, indptr, perm, x, g, grad_A, grad_x, status};
+    // four stages, four entries per gather round, grad_A written straight from the row threads:
+    // the best of the measured variants (staged + coalesced grad_A stores cost a third of the
+    // shared memory and with it the pipeline depth)
+    return spmv_pipe_launch<T, I, kBackwardSym, 4, 4, 3, true>(a, st);
+}
+
+#define NB200_INSTANTIATE_PIPE(T, I)                                                                                 \
+    template int spmv_pipe_forward<T, I>(int64_t, int64_t, int, const T*, const I*, const I*, const I*, const T*, T*, \
+                                         int32_t*, cudaStream_t);                                                    \
+    template int spmv_pipe_grad_A<T, I>(int64_t, int64_t, int, const I*, const I*, const T*, const T*, T*, int32_t*,  \
+                                        cudaStream_t);                                                               \
+    template int spmv_pipe_backward_sym<T, I>(int64_t, int64_t, int, const T*, const I*, const I*, const I*, const T*, \
+                                              const T*, T*, T*, int32_t*, cudaStream_t);
+NB200_INSTANTIATE_PIPE(float, int32_t)
+NB200_INSTANTIATE_PIPE(float, int64_t)
+NB200_INSTANTIATE_PIPE(double, int32_t)
+NB200_INSTANTIATE_PIPE(double, int64_t)
+
+}  // namespace nb200

@@ -17,6 +17,10 @@ from . import _cabi, _plan
 # structure: atomic-free, deterministic, bit-identical to the reference CPU loop) or "atomic"
 # (one fused pass over A with floating-point atomics).
 spmv_backward_mode = "transpose"
+# Which SpMV kernels run: "auto" picks the TMA-pipelined persistent kernels whenever the pattern is
+# regular enough (every block of 256 or 128 rows fits one pipeline stage) and the register-staged
+# streaming kernels otherwise; "stream" forces the latter.  Results are identical.
+spmv_kernel = "auto"
 
 
 def _dtype_code(t):
@@ -65,6 +69,17 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+_status_words = {}
+
+
+def _status_word(dev):
+    """One int32 device word per GPU into which kernels with bounded waits report a failure."""
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _status_words[key]
+
+
 # -------------------------------------------------------------------------------------------------
 # SpMV                                               reference cpp/sparse_csr.hpp:32-42
 # -------------------------------------------------------------------------------------------------
@@ -75,9 +90,10 @@ def spgemv_forward(A_rows, A_cols, A_data, A_col_ind, A_rowptr, x):
     plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_col_ind), _index_tensor(A_rowptr))
     idx, ptr, itype = plan.csr()
     with torch.cuda.device(dev):
+        block_rows = plan.spmv_block_rows() if spmv_kernel == "auto" else 0
         y = torch.empty(A_rows, dtype=A_data.dtype, device=dev)
         _cabi.call("nb200_spgemv_forward", A_rows, A_cols, plan.nnz, _ptr(A_data), _ptr(idx), _ptr(ptr),
-                   None, _ptr(x), _ptr(y), _dtype_code(A_data), itype, _stream())
+                   None, _ptr(x), _ptr(y), block_rows, _ptr(_status_word(dev)), _dtype_code(A_data), itype, _stream())
     return y
 
 
@@ -95,6 +111,10 @@ def spgemv_backward(grad_z, A_rows, A_cols, A_data, A_col_ind, A_rowptr, x):
     else:
         raise RuntimeError(f"unknown spmv_backward_mode {spmv_backward_mode!r}")
     with torch.cuda.device(dev):
+        auto = spmv_kernel == "auto"
+        block_rows = plan.spmv_block_rows() if auto else 0
+        t_block_rows = plan.spmv_block_rows(transposed=True) if (auto and t_indptr is not None) else 0
+        symmetric = int(auto and t_indptr is not None and block_rows > 0 and plan.pattern_symmetric())
         grad_A = torch.empty_like(A_data)
         grad_x = torch.empty(A_cols, dtype=A_data.dtype, device=dev)
         _cabi.call("nb200_spgemv_backward", A_rows, A_cols, plan.nnz, _ptr(A_data), _ptr(idx), _ptr(ptr),
@@ -102,7 +122,8 @@ def spgemv_backward(grad_z, A_rows, A_cols, A_data, A_col_ind, A_rowptr, x):
                    _ptr(t_indptr) if t_indptr is not None else None,
                    _ptr(t_indices) if t_indptr is not None else None,
                    _ptr(t_perm) if t_indptr is not None else None,
-                   _ptr(grad_A), _ptr(grad_x), _dtype_code(A_data), itype, _stream())
+                   _ptr(grad_A), _ptr(grad_x), block_rows, t_block_rows, symmetric, _ptr(_status_word(dev)),
+                   _dtype_code(A_data), itype, _stream())
     return [grad_A, grad_x]
 
 
@@ -261,14 +282,6 @@ def spgemm_backward(grad_C, C_indices, C_indptr, A_rows, A_cols, A_data, A_indic
 # device status word back (one small synchronising copy) so that an expired wait raises at once.
 sptrsv_wait_budget_cycles = 2_000_000_000
 sptrsv_check_status = True
-_status_words = {}
-
-
-def _status_word(dev):
-    key = dev.index if dev.index is not None else torch.cuda.current_device()
-    if key not in _status_words:
-        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=dev)
-    return _status_words[key]
 
 
 def check_status(device=None):

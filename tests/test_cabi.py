@@ -40,5 +40,5 @@ def test_version_and_status_strings():
 def test_argument_validation_needs_no_gpu():
     # negative sizes are rejected before any CUDA call is made
     handle = _cabi.lib()
-    assert handle.nb200_spgemv_forward(-1, 1, 0, None, None, None, None, None, None, 1, 1, None) == 1
+    assert handle.nb200_spgemv_forward(-1, 1, 0, None, None, None, None, None, None, 0, None, 1, 1, None) == 1
     assert handle.nb200_gather(-5, None, None, None, 0, 0, None) == 1

@@ -10,10 +10,16 @@ from numml_b200 import workloads as W
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def ops():
-    from numml_b200 import numml_torch_cpp
-    return numml_torch_cpp
+@pytest.fixture(params=["auto", "stream"])
+def ops(request):
+    """The operator module, once with automatic kernel choice (TMA-pipelined kernels where the
+    pattern allows) and once forced onto the register-staged streaming kernels."""
+    from numml_b200 import numml_torch_cpp, _plan
+    old = numml_torch_cpp.spmv_kernel
+    numml_torch_cpp.spmv_kernel = request.param
+    yield numml_torch_cpp
+    numml_torch_cpp.spmv_kernel = old
+    numml_torch_cpp.check_status()
 
 
 def dev(*ts):
@@ -140,6 +146,36 @@ def test_transpose_full_size_property(ops):
     assert torch.equal(torch.sort(perm).values, torch.arange(d.numel(), device="cuda"))
     d2, i2, p2, _ = ops.csr_transpose_forward(n, m, td, ti, tp)
     assert torch.equal(d2, dd) and torch.equal(i2, di) and torch.equal(p2, dp)
+
+
+def test_pipelined_kernels_are_chosen_for_stencils(ops):
+    from numml_b200 import _plan
+    d, i, p, (m, n) = W.poisson3d_7pt(24, torch.float64)
+    plan = _plan.get_plan(m, n, i.cuda(), p.cuda())
+    assert plan.spmv_block_rows() == 256 and plan.spmv_block_rows(transposed=True) == 256
+    d, i, p, (m, n) = W.random_csr(600, 5000, 0.02, seed=1)       # about 100 entries per row
+    assert _plan.get_plan(m, n, i.cuda(), p.cuda()).spmv_block_rows() == 0
+
+
+@pytest.mark.parametrize("n", [127, 255])
+def test_full_size_properties(ops, n):
+    """At benchmark scale (n^3 rows): A applied to the all-ones vector gives the row sums, which
+    for the Dirichlet Laplacian are the number of missing neighbours; forward and backward are
+    consistent: <A x, g> == <x, A^T g>; grad_A is the masked outer product."""
+    d, i, p, (m, k) = W.poisson3d_7pt(n, torch.float64)
+    dd, di, dp = d.cuda(), i.cuda(), p.cuda()
+    ones = torch.ones(k, dtype=torch.float64, device="cuda")
+    y = ops.spgemv_forward(m, k, dd, di, dp, ones)
+    counts = (dp[1:] - dp[:-1]).double()
+    assert torch.equal(y, 7.0 - counts)
+    x = torch.randn(k, dtype=torch.float64, device="cuda", generator=torch.Generator("cuda").manual_seed(0))
+    g = torch.randn(m, dtype=torch.float64, device="cuda", generator=torch.Generator("cuda").manual_seed(1))
+    Ax = ops.spgemv_forward(m, k, dd, di, dp, x)
+    gA, gx = ops.spgemv_backward(g, m, k, dd, di, dp, x)
+    lhs, rhs = torch.dot(Ax, g).item(), torch.dot(x, gx).item()
+    assert abs(lhs - rhs) <= 1e-11 * abs(lhs)
+    rows = torch.repeat_interleave(torch.arange(m, device="cuda"), dp[1:] - dp[:-1])
+    assert torch.equal(gA, g[rows] * x[di])
 
 
 def test_cpu_tensors_are_rejected(ops):
