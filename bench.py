@@ -42,6 +42,18 @@ def algorithmic_bytes(rows, cols, nnz, s, w):
     return fwd, bwd
 
 
+def ncu_traffic(kernel_key, nnz):
+    """DRAM bytes per launch of the named kernel from the committed ncu capture (taken on the
+    128^3 workload; scaled by nnz for other grid sizes, traffic being proportional to it)."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        with open(path) as f:
+            t = json.load(f)[kernel_key]
+        return int((t["read"] + t["write"]) * (nnz / 14581760.0))
+    except (OSError, KeyError, ValueError):
+        return None
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -65,7 +77,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -379,8 +391,12 @@ def single_gpu_steps(A, x_h, g_h, dev, ops, _plan, _cabi, P, stream):
         dominant = bwd_name if t_b >= t_f else "spmv_forward"
         bytes_, t = (bwd_b, t_b) if t_b >= t_f else (fwd_b, t_f)
         ach = bytes_ / (t * 1e-6) / 1e9
+        if t_b >= t_f:
+            key = "spmv_backward_fused_symmetric" if sym else ("spmv_backward_two_pass_stream" if not br else None)
+        else:
+            key = "spmv_forward_pipelined" if br else "spmv_forward_stream"
         return {"bound": "hbm", "kernel": dominant, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                "peak_source": peak_kind + " (copy bandwidth)", "traffic": None,
+                "peak_source": peak_kind + " (copy bandwidth)", "traffic": ncu_traffic(key, nnz) if key else None,
                 "launch_us": t, "algorithmic_bytes": bytes_,
                 "forward": {"us": t_f, "GBps": fwd_b / (t_f * 1e-6) / 1e9, "frac": fwd_b / (t_f * 1e-6) / 1e9 / peak},
                 "backward": {"us": t_b, "GBps": bwd_b / (t_b * 1e-6) / 1e9, "frac": bwd_b / (t_b * 1e-6) / 1e9 / peak}}

@@ -101,6 +101,15 @@ NB200_API int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
                           int block_rows, int t_block_rows, int pattern_symmetric, int32_t* status,
                           int dtype, int itype, nb200_stream stream);
 
+/* grad_A[k] = g[row(k)] * x[col(k)] alone: the masked outer product of spgemv_backward (reference
+ * cpp/sparse_csr_cpu.cpp:59-65, cuda_kernel_masked_outerproduct cpp/sparse_csr_cuda.cu:76-95), for
+ * callers that schedule the two halves of the backward themselves.  `indptr` may point into the
+ * middle of a row-pointer array (a contiguous range of rows; entries are absolute positions). */
+NB200_API int nb200_spgemv_grad_A(int64_t rows, int64_t cols, int64_t nnz,
+                                  const void* indices, const void* indptr, const void* x, const void* g,
+                                  void* grad_A, int block_rows, int32_t* status,
+                                  int dtype, int itype, nb200_stream stream);
+
 /* ---------------------------------------------------------------------------------------------
  * CSR transpose (structure).      Replaces csr_transpose_forward (reference
  * cpp/sparse_csr.hpp:57-60, CPU cpp/sparse_csr_cpu.cpp:311-367, CUDA cpp/sparse_csr_cuda.cu:176-279).

@@ -367,6 +367,43 @@ extern "C" int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
 }
 
 
+// grad_A alone (the masked outer product g x^T on the pattern), for callers that schedule the
+// two halves of the backward separately (the row-partitioned driver overlaps them with its
+// halo exchange).
+extern "C" int nb200_spgemv_grad_A(int64_t rows, int64_t cols, int64_t nnz,
+                                   const void* indices, const void* indptr, const void* x, const void* g,
+                                   void* grad_A, int block_rows, int32_t* status,
+                                   int dtype, int itype, nb200_stream stream) {
+    (void)cols;
+    if (rows < 0 || nnz < 0 || block_rows < 0 || block_rows > 256) return NB200_ERR_BAD_ARG;
+    if (rows == 0 || nnz == 0) return NB200_OK;
+    if (!indices || !indptr || !x || !g || !grad_A) return NB200_ERR_BAD_ARG;
+    if (!aligned16(indices) || !aligned16(grad_A)) return NB200_ERR_ALIGN;
+    if (itype == NB200_I32 && nnz > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
+    cudaStream_t st = as_stream(stream);
+    return NB200_DISPATCH(dtype, itype, ([&]() -> int {
+        if (block_rows > 0)
+            return spmv_pipe_grad_A<T, I>(rows, nnz, block_rows, (const I*)indices, (const I*)indptr, (const T*)x,
+                                          (const T*)g, (T*)grad_A, status, st);
+        const double mean = (double)nnz / (double)rows;
+        if (mean <= kStreamMaxMeanRow) {
+            const int rpc = stream_rows_per_cta(rows, nnz);
+            const int64_t grid = ceil_div(rows, (int64_t)rpc);
+            if (grid > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
+            spmv_bwd_stream_kernel<T, I, kStreamThreads, kStreamU, false><<<(unsigned)grid, kStreamThreads, 0, st>>>(
+                rows, nnz, rpc, (const T*)nullptr, (const I*)indices, (const I*)indptr, (const T*)x, (const T*)g,
+                (T*)grad_A, (T*)nullptr);
+        } else {
+            const int64_t want = ceil_div(rows, (int64_t)8);
+            const unsigned grid = (unsigned)min(want, (int64_t)kSMs * 64);
+            spmv_bwd_vector_kernel<T, I, false><<<grid, 256, 0, st>>>(rows, (const T*)nullptr, (const I*)indices,
+                                                                      (const I*)indptr, (const T*)x, (const T*)g,
+                                                                      (T*)grad_A, (T*)nullptr);
+        }
+        return launch_status();
+    }()));
+}
+
 // ---------------------------------------------------------------------------------------------
 // Block profile: the largest number of entries in any block of R consecutive rows, for
 // R = 256, 128, 64, 32.  The host picks the largest R whose maximum fits one pipeline stage.

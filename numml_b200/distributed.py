@@ -282,6 +282,116 @@ def dist_spgemm(A, B):
                                 n_ext, B.global_shape[1], ext_data, ext_indices, ext_indptr)
 
 
+class DistSpMVEngine:
+    """Forward + backward of a row-partitioned SpMV as a fixed schedule of C-ABI launches over
+    preallocated buffers, with the halo exchange overlapped with the rows that do not need it.
+
+    forward:   pack -> [exchange || rows without halo columns] -> remaining rows
+    backward:  grad_x partial sums of the halo columns -> [exchange || grad_A pass, local grad_x
+               pass] -> add the received partial sums (peers in ascending order)
+
+    The outputs live in the engine's buffers (``y``, ``grad_A``, ``grad_x``); x is written by the
+    caller into ``x_ext[:n_local]``.  CUDA only.
+    """
+
+    def __init__(self, A):
+        import ctypes
+        from . import _cabi, _plan
+        self._c, self._cabi = ctypes, _cabi
+        self.A = A
+        halo = A.halo
+        dev = A.data.device
+        dt = A.data.dtype
+        self.n, self.n_ext, self.nnz = A.n_rows, halo.n_local + halo.n_halo, int(A.data.numel())
+        self.code = _cabi.F64 if dt == torch.float64 else _cabi.F32
+        plan = _plan.get_plan(self.n, self.n_ext, A.indices, A.indptr)
+        self.plan = plan
+        self.idx, self.ptr, self.itype = plan.csr()
+        self.t_indptr, self.t_indices, self.t_perm, _ = plan.transpose()
+        self.br = plan.spmv_block_rows()
+        self.tbr = plan.spmv_block_rows(transposed=True)
+        self.esize = self.ptr.element_size()
+        self.vsize = A.data.element_size()
+        # rows that reference no halo column, as one contiguous range aligned to the kernel's row blocks
+        counts = torch.zeros(self.n + 1, dtype=torch.int64, device=dev)
+        counts[1:] = torch.cumsum((A.indices >= halo.n_local).to(torch.int64), 0)[A.indptr[1:] - 1] if self.nnz else 0
+        has_halo = (counts[1:] - counts[:-1]) > 0 if self.nnz else torch.zeros(self.n, dtype=torch.bool, device=dev)
+        marks = [-1] + torch.nonzero(has_halo).flatten().tolist() + [self.n]
+        gaps = [(marks[q + 1] - marks[q] - 1, marks[q] + 1, marks[q + 1]) for q in range(len(marks) - 1)]
+        _, a, b = max(gaps)
+        align = 256
+        a = min(self.n, -(-a // align) * align)
+        b = max(a, (b // align) * align)
+        self.interior = (a, b)
+        self.x_ext = torch.zeros(self.n_ext, dtype=dt, device=dev)
+        self.gx_ext = torch.zeros(self.n_ext, dtype=dt, device=dev)
+        self.y = torch.empty(self.n, dtype=dt, device=dev)
+        self.grad_A = torch.empty(self.nnz, dtype=dt, device=dev)
+        self.grad_x = self.gx_ext[:halo.n_local]
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.send_bufs = {p: torch.empty(halo.send_counts[p], dtype=dt, device=dev) for p in halo.peers_out}
+        self.recv_bufs = {p: torch.empty(halo.send_counts[p], dtype=dt, device=dev) for p in halo.peers_out}
+        self.launches_per_step = 3 + 3 + len(halo.peers_out)
+
+    def _p(self, t, offset_elems=0):
+        return self._c.c_void_p(t.data_ptr() + offset_elems * t.element_size())
+
+    def _stream(self):
+        return self._c.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _fwd_rows(self, a, b, ptr, idx, perm, vec, out, out_off, rows_total_cols, hint):
+        if b <= a:
+            return
+        self._cabi.call("nb200_spgemv_forward", b - a, rows_total_cols, self.nnz, self._p(self.A.data), self._p(idx),
+                        self._p(ptr, a), self._p(perm) if perm is not None else None, self._p(vec),
+                        self._p(out, out_off + a), hint if a % 256 == 0 else 0, self._p(self.status), self.code,
+                        self.itype, self._stream())
+
+    def forward(self):
+        """y = A x with x taken from x_ext[:n_local]."""
+        halo = self.A.halo
+        ops = []
+        for p in halo.peers_out:
+            self._cabi.call("nb200_gather", halo.send_counts[p], self._p(self.x_ext), self._p(halo.send[p]),
+                            self._p(self.send_bufs[p]), self.code, self._cabi.I64, self._stream())
+            ops.append(dist.P2POp(dist.isend, self.send_bufs[p], halo._peer(p), group=halo.group))
+        for p in halo.peers_in:
+            o = halo.n_local + halo.recv_offsets[p]
+            ops.append(dist.P2POp(dist.irecv, self.x_ext[o:o + halo.recv_counts[p]], halo._peer(p), group=halo.group))
+        reqs = dist.batch_isend_irecv(ops) if ops else []
+        a, b = self.interior
+        self._fwd_rows(a, b, self.ptr, self.idx, None, self.x_ext, self.y, 0, self.n_ext, self.br)
+        for r in reqs:
+            r.wait()
+        self._fwd_rows(0, a, self.ptr, self.idx, None, self.x_ext, self.y, 0, self.n_ext, self.br)
+        self._fwd_rows(b, self.n, self.ptr, self.idx, None, self.x_ext, self.y, 0, self.n_ext, self.br)
+        return self.y
+
+    def backward(self, g):
+        """grad_A (pattern of the local rows) and grad_x (local block) for upstream gradient g;
+        x_ext must still hold the forward's values."""
+        halo = self.A.halo
+        nl = halo.n_local
+        # partial sums for halo columns first, so that their exchange overlaps the rest
+        self._fwd_rows(nl, self.n_ext, self.t_indptr, self.t_indices, self.t_perm, g, self.gx_ext, 0, self.n, self.tbr)
+        ops = []
+        for p in halo.peers_in:
+            o = nl + halo.recv_offsets[p]
+            ops.append(dist.P2POp(dist.isend, self.gx_ext[o:o + halo.recv_counts[p]], halo._peer(p), group=halo.group))
+        for p in halo.peers_out:
+            ops.append(dist.P2POp(dist.irecv, self.recv_bufs[p], halo._peer(p), group=halo.group))
+        reqs = dist.batch_isend_irecv(ops) if ops else []
+        self._cabi.call("nb200_spgemv_grad_A", self.n, self.n_ext, self.nnz, self._p(self.idx), self._p(self.ptr),
+                        self._p(self.x_ext), self._p(g), self._p(self.grad_A), self.br, self._p(self.status),
+                        self.code, self.itype, self._stream())
+        self._fwd_rows(0, nl, self.t_indptr, self.t_indices, self.t_perm, g, self.gx_ext, 0, self.n, self.tbr)
+        for r in reqs:
+            r.wait()
+        for p in halo.peers_out:
+            self.grad_x.index_add_(0, halo.send[p], self.recv_bufs[p])
+        return self.grad_A, self.grad_x
+
+
 def bench_steps(n, rank, world, dev, ops):
     """Benchmark closures for bench.py at world > 1: every rank owns one n^3 slab (z-planes
     rank*n .. (rank+1)*n) of the 7-point Laplacian on an n x n x (n*world) grid."""
@@ -292,14 +402,14 @@ def bench_steps(n, rank, world, dev, ops):
     A = DistSparseCSR(d.to(dev), i.to(dev), p.to(dev), (rows_per * world, rows_per * world), bounds, ops=ops)
     x_h = W.randn(rows_per, 100 + rank, torch.float64)
     g_h = W.randn(rows_per, 200 + rank, torch.float64)
-    x, g = x_h.to(dev), g_h.to(dev)
+    g = g_h.to(dev)
+    engine = DistSpMVEngine(A)
+    engine.x_ext[:rows_per] = x_h.to(dev)
     A.requires_grad = True
 
     def step_dev():
-        xg = x.detach().requires_grad_(True)
-        A.data.grad = None
-        y = A @ xg
-        y.backward(g)
+        engine.forward()
+        engine.backward(g)
 
     x_pin, g_pin = x_h.pin_memory(), g_h.pin_memory()
     y_pin = torch.empty(rows_per, dtype=torch.float64).pin_memory()
@@ -319,6 +429,7 @@ def bench_steps(n, rank, world, dev, ops):
 
     n_ext = A.halo.n_local + A.halo.n_halo
     info = {"nnz": int(d.numel()), "rows": rows_per, "cols": n_ext, "index_bytes": 4,
-            "launches_per_step": 3 + len(A.halo.peers_out),     # forward, grad_A pass, grad_x pass, one pack per peer
+            "launches_per_step": engine.launches_per_step, "status_word": engine.status,
+            "kernels": "tma-pipelined" if engine.br else "register-staged",
             "h2d_bytes": 2 * rows_per * 8, "d2h_bytes": (2 * rows_per + int(d.numel())) * 8, "roofline": None}
     return step_dev, step_e2e, info

@@ -38,6 +38,16 @@ def _worker(rank, world, init_file):
         assert torch.equal(y.detach().cpu(), y_ref[lo:hi])
         assert torch.equal(A.data.grad.cpu(), gA_ref[sl])
         assert torch.allclose(xl.grad.cpu(), gx_ref[lo:hi], rtol=1e-13, atol=1e-13)
+        # the pre-planned engine (overlapped exchange, sub-range launches) gives the same results
+        eng = nd.DistSpMVEngine(A)
+        eng.x_ext[:hi - lo] = x[lo:hi].to(dev)
+        for _ in range(2):
+            y2 = eng.forward()
+            gA2, gx2 = eng.backward(g[lo:hi].to(dev))
+        assert torch.equal(y2.cpu(), y_ref[lo:hi])
+        assert torch.equal(gA2.cpu(), gA_ref[sl])
+        assert torch.allclose(gx2.cpu(), gx_ref[lo:hi], rtol=1e-13, atol=1e-13)
+        assert int(eng.status.item()) == 0
         Cd, Ci, Cp = A @ A
         C_ref = oracle.spgemm_forward(m, n, d, i, p, m, n, d, i, p)
         assert torch.equal(Cp.cpu(), C_ref[2][lo:hi + 1] - C_ref[2][lo])
