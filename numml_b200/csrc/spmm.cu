@@ -11,6 +11,13 @@
 // structure without atomics.
 #include "common.cuh"
 
+#ifndef NB200_SPMM_GRAD_BATCH
+#define NB200_SPMM_GRAD_BATCH 4   // entries reduced together in the grad_A kernel (4 or 8)
+#endif
+#ifndef NB200_SPMM_BATCH
+#define NB200_SPMM_BATCH 4   // rows of B requested together per lane group in the forward kernel
+#endif
+
 namespace nb200 {
 
 template <typename T, int VEC> struct Vec;
@@ -75,15 +82,31 @@ spdmm_forward_kernel(int64_t rows, int64_t K, const T* __restrict__ data, const 
                 v_mine = PERM ? ldg(data + perm[k]) : data[k];
             }
             const int cnt = (int)min((int64_t)G, e - s - off);   // <= 0 for groups that are done
-#pragma unroll 4
-            for (int j = 0; j < G; ++j) {
-                const I c = __shfl_sync(0xffffffffu, c_mine, gbase + j);
-                const T v = __shfl_sync(0xffffffffu, v_mine, gbase + j);
-                if (j < cnt && col_ok) {
-                    T b[VEC];
-                    load_vec<T, VEC>(B + (int64_t)c * K + col, b);
+            // batches of BATCH entries: broadcast (column, value), issue all row loads, then accumulate in order
+            constexpr int BATCH = NB200_SPMM_BATCH;
+            int cnt_w = cnt;                                  // warp-uniform trip count
 #pragma unroll
-                    for (int q = 0; q < VEC; ++q) acc[q] = add_rn(acc[q], mul_rn(v, b[q]));
+            for (int o = G; o < 32; o <<= 1) cnt_w = max(cnt_w, __shfl_xor_sync(0xffffffffu, cnt_w, o));
+#pragma unroll 1
+            for (int j0 = 0; j0 < cnt_w; j0 += BATCH) {
+                I c[BATCH];
+                T v[BATCH];
+                T b[BATCH][VEC];
+#pragma unroll
+                for (int q = 0; q < BATCH; ++q) {
+                    c[q] = __shfl_sync(0xffffffffu, c_mine, gbase + j0 + q);
+                    v[q] = __shfl_sync(0xffffffffu, v_mine, gbase + j0 + q);
+                }
+#pragma unroll
+                for (int q = 0; q < BATCH; ++q) {
+                    if (j0 + q < cnt && col_ok) load_vec<T, VEC>(B + (int64_t)c[q] * K + col, b[q]);
+                }
+#pragma unroll
+                for (int q = 0; q < BATCH; ++q) {
+                    if (j0 + q < cnt && col_ok) {
+#pragma unroll
+                        for (int t = 0; t < VEC; ++t) acc[t] = add_rn(acc[t], mul_rn(v[q], b[q][t]));
+                    }
                 }
             }
         }
@@ -117,6 +140,64 @@ spdmm_grad_A_kernel(int64_t rows, int64_t K, const I* __restrict__ indices, cons
     int64_t len = e - s;
 #pragma unroll
     for (int o = G; o < 32; o <<= 1) len = max(len, __shfl_xor_sync(0xffffffffu, len, o));
+
+    if (single_tile) {
+        // GB entries at a time: their rows of B are requested before any arithmetic, each lane forms
+        // GB partial dot products over its slice, and the GB sums are reduced together by recursive
+        // halving (GB/2 + ... + 1 exchanges, then log2(G/GB) more) instead of GB separate butterflies.
+        const bool col_ok = (int64_t)gl * VEC < K;
+        constexpr int GB = NB200_SPMM_GRAD_BATCH;
+        for (int64_t off = 0; off < len; off += G) {
+            const int64_t k = s + off + gl;
+            const I c_mine = (k < e) ? indices[k] : (I)0;
+            const int cnt = (int)min((int64_t)G, e - s - off);
+            T out_mine = 0;
+            int cnt_w = cnt;                                  // warp-uniform trip count
+#pragma unroll
+            for (int o = G; o < 32; o <<= 1) cnt_w = max(cnt_w, __shfl_xor_sync(0xffffffffu, cnt_w, o));
+#pragma unroll 1
+            for (int j0 = 0; j0 < cnt_w; j0 += GB) {
+                T b[GB][VEC];
+                T p[GB];
+#pragma unroll
+                for (int q = 0; q < GB; ++q) {
+                    const I c = __shfl_sync(0xffffffffu, c_mine, gbase + j0 + q);
+#pragma unroll
+                    for (int t = 0; t < VEC; ++t) b[q][t] = 0;
+                    if (j0 + q < cnt && col_ok) load_vec<T, VEC>(B + (int64_t)c * K + (int64_t)gl * VEC, b[q]);
+                }
+#pragma unroll
+                for (int q = 0; q < GB; ++q) {
+                    p[q] = 0;
+#pragma unroll
+                    for (int t = 0; t < VEC; ++t) p[q] += g0[t] * b[q][t];
+                }
+                // halving steps: after the step with offset o, lanes with that bit set keep the upper half
+#pragma unroll
+                for (int m = GB, o = G / 2; m > 1; m >>= 1, o >>= 1) {
+                    const bool up = (gl & o) != 0;
+#pragma unroll
+                    for (int i = 0; i < m / 2; ++i) {
+                        const T send = up ? p[i] : p[i + m / 2];
+                        const T keep = up ? p[i + m / 2] : p[i];
+                        p[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+                    }
+                }
+#pragma unroll
+                for (int o = G / (2 * GB); o > 0; o >>= 1) p[0] += __shfl_xor_sync(0xffffffffu, p[0], o);
+                // the lane whose top log2(GB) bits spell q holds entry q; route it to lane j0 + q
+                const int q = (gl - j0) & (GB - 1);
+                int src = 0;
+#pragma unroll
+                for (int bit = GB / 2, o = G / 2; bit > 0; bit >>= 1, o >>= 1) src += (q & bit) ? o : 0;
+                const T v = __shfl_sync(0xffffffffu, p[0], gbase + src);
+                if (gl >= j0 && gl < j0 + GB) out_mine = v;
+            }
+            if (k < e) grad_A[k] = out_mine;
+        }
+        return;
+    }
+
     for (int64_t off = 0; off < len; off += G) {
         const int64_t k = s + off + gl;
         const I c_mine = (k < e) ? indices[k] : (I)0;
