@@ -260,12 +260,30 @@ spgemm_numeric_kernel(const int32_t* __restrict__ list, const unsigned long long
             }
         }
         team_sync<TEAM>();
-        if (usable) team_sort<T, TEAM, true>(keys, vals, table, t);
-        if (active && usable) {
-            const int64_t o0 = C_indptr[row], n = C_indptr[row + 1] - o0;
-            for (int64_t q = t; q < n; q += TEAM) {
-                C_indices[o0 + q] = (int64_t)keys[q];
-                C_data[o0 + q] = vals[q];
+        if (!SPILL && TABLE <= 64) {
+            // tiny tables: the position of a column in the sorted row is the number of smaller
+            // columns in the table (empty slots hold the largest key); no sort, no data movement
+            if (active) {
+                const int64_t o0 = C_indptr[row];
+                for (int sl = t; sl < TABLE; sl += TEAM) {
+                    const uint32_t key = keys[sl];
+                    if (key != kEmptyKey) {
+                        int rank = 0;
+#pragma unroll 8
+                        for (int q = 0; q < TABLE; ++q) rank += keys[q] < key;
+                        C_indices[o0 + rank] = (int64_t)key;
+                        C_data[o0 + rank] = vals[sl];
+                    }
+                }
+            }
+        } else {
+            if (usable) team_sort<T, TEAM, true>(keys, vals, table, t);
+            if (active && usable) {
+                const int64_t o0 = C_indptr[row], n = C_indptr[row + 1] - o0;
+                for (int64_t q = t; q < n; q += TEAM) {
+                    C_indices[o0 + q] = (int64_t)keys[q];
+                    C_data[o0 + q] = vals[q];
+                }
             }
         }
         team_sync<TEAM>();
