@@ -101,6 +101,17 @@ NB200_API int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
                           int block_rows, int t_block_rows, int pattern_symmetric, int32_t* status,
                           int dtype, int itype, nb200_stream stream);
 
+/* The one-pass backward of nb200_spgemv_backward for a square matrix whose pattern equals its
+ * transpose (so t_indptr == indptr, t_indices == indices and only t_perm is needed), restricted to
+ * rows [row_begin, row_end): grad_A[k] for the entries of those rows and grad_x[i] for those i.
+ * Every pointer is the base of its array (absolute indexing).  Used by the row-partitioned driver,
+ * which runs the rows feeding its exchange first.  Needs block_rows in 1..256 as described above. */
+NB200_API int nb200_spgemv_backward_symmetric_rows(int64_t n, int64_t nnz, int64_t row_begin, int64_t row_end,
+                                                   const void* data, const void* indices, const void* indptr,
+                                                   const void* t_perm, const void* x, const void* g,
+                                                   void* grad_A, void* grad_x, int block_rows, int32_t* status,
+                                                   int dtype, int itype, nb200_stream stream);
+
 /* grad_A[k] = g[row(k)] * x[col(k)] alone: the masked outer product of spgemv_backward (reference
  * cpp/sparse_csr_cpu.cpp:59-65, cuda_kernel_masked_outerproduct cpp/sparse_csr_cuda.cu:76-95), for
  * callers that schedule the two halves of the backward themselves.  `indptr` may point into the

@@ -21,6 +21,8 @@ SIGNATURES = {
     "nb200_spgemv_forward": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp, _int, _int, _vp]),
     "nb200_spgemv_backward": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _int,
                                      _vp, _int, _int, _vp]),
+    "nb200_spgemv_backward_symmetric_rows": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int,
+                                                    _vp, _int, _int, _vp]),
     "nb200_spgemv_grad_A": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _vp, _int, _int, _vp]),
     "nb200_csr_block_profile": (_int, [_i64, _vp, _int, _vp, _vp]),
     "nb200_spmv_pipeline_tile": (_int, []),

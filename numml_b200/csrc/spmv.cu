@@ -286,7 +286,7 @@ int spmv_backward_launch(int64_t rows, int64_t cols, int64_t nnz, const T* data,
                          bool pattern_symmetric, int32_t* status, cudaStream_t st) {
     const bool atomic = (t_indptr == nullptr);
     if (!atomic && pattern_symmetric && block_rows > 0 && rows == cols && nnz > 0)
-        return spmv_pipe_backward_sym<T, I>(rows, nnz, block_rows, data, indices, indptr, t_perm, x, g, grad_A, grad_x,
+        return spmv_pipe_backward_sym<T, I>(0, rows, nnz, block_rows, data, indices, indptr, t_perm, x, g, grad_A, grad_x,
                                             status, st);
     if (atomic && cols > 0) {
         if (cudaMemsetAsync(grad_x, 0, sizeof(T) * (size_t)cols, st) != cudaSuccess) return NB200_ERR_CUDA;
@@ -366,6 +366,26 @@ extern "C" int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
                                     pattern_symmetric != 0, status, as_stream(stream))));
 }
 
+
+// The fused one-pass backward on a contiguous range of rows of a matrix whose pattern equals its
+// transpose.  All arrays are indexed absolutely; a row-partitioned driver runs the rows that feed
+// its exchange first and the rest while the exchange is in flight.
+extern "C" int nb200_spgemv_backward_symmetric_rows(int64_t n, int64_t nnz, int64_t row_begin, int64_t row_end,
+                                                    const void* data, const void* indices, const void* indptr,
+                                                    const void* t_perm, const void* x, const void* g,
+                                                    void* grad_A, void* grad_x, int block_rows, int32_t* status,
+                                                    int dtype, int itype, nb200_stream stream) {
+    if (n < 0 || nnz < 0 || row_begin < 0 || row_end < row_begin || row_end > n) return NB200_ERR_BAD_ARG;
+    if (block_rows < 1 || block_rows > 256) return NB200_ERR_BAD_ARG;
+    if (row_end == row_begin || nnz == 0) return NB200_OK;
+    if (!data || !indices || !indptr || !t_perm || !x || !g || !grad_A || !grad_x) return NB200_ERR_BAD_ARG;
+    if (!aligned16(indices) || !aligned16(t_perm)) return NB200_ERR_ALIGN;
+    if (itype == NB200_I32 && nnz > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
+    return NB200_DISPATCH(dtype, itype,
+        (spmv_pipe_backward_sym<T, I>(row_begin, row_end, nnz, block_rows, (const T*)data, (const I*)indices,
+                                      (const I*)indptr, (const I*)t_perm, (const T*)x, (const T*)g, (T*)grad_A,
+                                      (T*)grad_x, status, as_stream(stream))));
+}
 
 // grad_A alone (the masked outer product g x^T on the pattern), for callers that schedule the
 // two halves of the backward separately (the row-partitioned driver overlaps them with its

@@ -64,7 +64,8 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;"
 
 template <typename T, typename I>
 struct PipeArgs {
-    int64_t rows, nnz, num_blocks;
+    int64_t row0;        // first row handled by this launch (blocks are counted from here)
+    int64_t rows, nnz, num_blocks;   // rows = one past the last row handled
     int block_rows;
     const T* data;       // values of A
     const I* indices;    // column of each staged entry
@@ -153,7 +154,7 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
         auto block_range = [&](int64_t blk, int64_t& begin_, int64_t& end_) {
             begin_ = 0; end_ = 0;
             if (blk < a.num_blocks) {
-                const int64_t q0 = blk * a.block_rows, q1 = min(q0 + (int64_t)a.block_rows, a.rows);
+                const int64_t q0 = a.row0 + blk * a.block_rows, q1 = min(q0 + (int64_t)a.block_rows, a.rows);
                 begin_ = (int64_t)a.indptr[q0];
                 end_ = (int64_t)a.indptr[q1];
             }
@@ -197,7 +198,7 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
     auto fetch = [&](int64_t blk) {
         BlockInfo f{0, 0, 0, 0, (T)0};
         if (blk < a.num_blocks) {
-            const int64_t r0 = blk * a.block_rows, r1 = min(r0 + (int64_t)a.block_rows, a.rows);
+            const int64_t r0 = a.row0 + blk * a.block_rows, r1 = min(r0 + (int64_t)a.block_rows, a.rows);
             f.begin = (int64_t)a.indptr[r0];
             f.end = (int64_t)a.indptr[r1];
             const int64_t r = r0 + tid;
@@ -217,7 +218,7 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
         const unsigned ph = (unsigned)((it / kPipeStages) & 1);
         const BlockInfo nxt = fetch(b + gridDim.x);
 
-        const int64_t r0 = b * a.block_rows, r1 = min(r0 + (int64_t)a.block_rows, a.rows);
+        const int64_t r0 = a.row0 + b * a.block_rows, r1 = min(r0 + (int64_t)a.block_rows, a.rows);
         const int64_t begin = cur.begin, end = cur.end;
         const int64_t base = begin & ~(int64_t)3;
         const int64_t bulk_stop = min(min((end + 3) & ~(int64_t)3, nnz_bulk_end), base + kPipeTile);
@@ -337,21 +338,23 @@ int spmv_pipe_launch(const PipeArgs<T, I>& args, cudaStream_t st) {
 template <typename T, typename I>
 int spmv_pipe_forward(int64_t rows, int64_t nnz, int block_rows, const T* data, const I* indices, const I* indptr,
                       const I* perm, const T* x, T* y, int32_t* status, cudaStream_t st) {
-    PipeArgs<T, I> a{rows, nnz, ceil_div(rows, (int64_t)block_rows), block_rows, data, indices, indptr, perm, x, nullptr, y, nullptr, status};
+    PipeArgs<T, I> a{0, rows, nnz, ceil_div(rows, (int64_t)block_rows), block_rows, data, indices, indptr, perm, x, nullptr, y, nullptr, status};
     return perm ? spmv_pipe_launch<T, I, kForwardPerm, 3>(a, st) : spmv_pipe_launch<T, I, kForward, 3>(a, st);
 }
 
 template <typename T, typename I>
 int spmv_pipe_grad_A(int64_t rows, int64_t nnz, int block_rows, const I* indices, const I* indptr, const T* x,
                      const T* g, T* grad_A, int32_t* status, cudaStream_t st) {
-    PipeArgs<T, I> a{rows, nnz, ceil_div(rows, (int64_t)block_rows), block_rows, nullptr, indices, indptr, nullptr, x, g, grad_A, nullptr, status};
+    PipeArgs<T, I> a{0, rows, nnz, ceil_div(rows, (int64_t)block_rows), block_rows, nullptr, indices, indptr, nullptr, x, g, grad_A, nullptr, status};
     return spmv_pipe_launch<T, I, kGradA, 3>(a, st);
 }
 
 template <typename T, typename I>
-int spmv_pipe_backward_sym(int64_t rows, int64_t nnz, int block_rows, const T* data, const I* indices, const I* indptr,
-                           const I* perm, const T* x, const T* g, T* grad_A, T* grad_x, int32_t* status, cudaStream_t st) {
-    PipeArgs<T, I> a{rows, nnz, ceil_div(rows, (int64_t)block_rows), block_rows, data, indices, indptr, perm, x, g, grad_A, grad_x, status};
+int spmv_pipe_backward_sym(int64_t row_begin, int64_t row_end, int64_t nnz, int block_rows, const T* data,
+                           const I* indices, const I* indptr, const I* perm, const T* x, const T* g, T* grad_A,
+                           T* grad_x, int32_t* status, cudaStream_t st) {
+    if (row_end <= row_begin) return NB200_OK;
+    PipeArgs<T, I> a{row_begin, row_end, nnz, ceil_div(row_end - row_begin, (int64_t)block_rows), block_rows, data, indices, indptr, perm, x, g, grad_A, grad_x, status};
     // four stages, four entries per gather round, grad_A written straight from the row threads:
     // the best of the measured variants (staged + coalesced grad_A stores cost a third of the
     // shared memory and with it the pipeline depth)
@@ -363,8 +366,8 @@ int spmv_pipe_backward_sym(int64_t rows, int64_t nnz, int block_rows, const T* d
                                          int32_t*, cudaStream_t);                                                    \
     template int spmv_pipe_grad_A<T, I>(int64_t, int64_t, int, const I*, const I*, const T*, const T*, T*, int32_t*,  \
                                         cudaStream_t);                                                               \
-    template int spmv_pipe_backward_sym<T, I>(int64_t, int64_t, int, const T*, const I*, const I*, const I*, const T*, \
-                                              const T*, T*, T*, int32_t*, cudaStream_t);
+    template int spmv_pipe_backward_sym<T, I>(int64_t, int64_t, int64_t, int, const T*, const I*, const I*, const I*, \
+                                              const T*, const T*, T*, T*, int32_t*, cudaStream_t);
 NB200_INSTANTIATE_PIPE(float, int32_t)
 NB200_INSTANTIATE_PIPE(float, int64_t)
 NB200_INSTANTIATE_PIPE(double, int32_t)

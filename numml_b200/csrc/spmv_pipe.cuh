@@ -20,8 +20,10 @@ int spmv_pipe_grad_A(int64_t rows, int64_t nnz, int block_rows, const I* indices
 // Whole backward in one pass for a pattern that equals its transpose (t_indptr == indptr and
 // t_indices == indices, so only the permutation of the transposed structure is needed):
 // grad_A[k] = g[row(k)] x[col(k)] and grad_x[i] = sum_k data[perm[k]] g[col(k)] over row i.
+// Handles rows [row_begin, row_end); every array is indexed absolutely.
 template <typename T, typename I>
-int spmv_pipe_backward_sym(int64_t rows, int64_t nnz, int block_rows, const T* data, const I* indices, const I* indptr,
-                           const I* perm, const T* x, const T* g, T* grad_A, T* grad_x, int32_t* status, cudaStream_t st);
+int spmv_pipe_backward_sym(int64_t row_begin, int64_t row_end, int64_t nnz, int block_rows, const T* data,
+                           const I* indices, const I* indptr, const I* perm, const T* x, const T* g, T* grad_A,
+                           T* grad_x, int32_t* status, cudaStream_t st);
 
 }  // namespace nb200

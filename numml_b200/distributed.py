@@ -332,59 +332,149 @@ class DistSpMVEngine:
         self.send_bufs = {p: torch.empty(halo.send_counts[p], dtype=dt, device=dev) for p in halo.peers_out}
         self.recv_bufs = {p: torch.empty(halo.send_counts[p], dtype=dt, device=dev) for p in halo.peers_out}
         self.launches_per_step = 3 + 3 + len(halo.peers_out)
+        self.fused = False
+        if self.br > 0 and self.n == halo.n_local and self.nnz > 0:
+            self._build_symmetric_extension(_plan)
+
+    def _build_symmetric_extension(self, _plan):
+        """Make the local block square and pattern-symmetric by appending one ghost row per halo
+        column holding the transposed halo entries.  The one-pass backward kernel then produces,
+        from the ghost rows, exactly the partial sums of grad_x that belong to the neighbours, and
+        from the local rows grad_A and the local part of grad_x.  Ghost entries carry no values:
+        a ghost row reads the values of the local entries it mirrors through the permutation, and
+        a local entry in a halo column is paired with itself and multiplied by the zero that the
+        extended upstream gradient holds there."""
+        A, halo = self.A, self.A.halo
+        dev = A.data.device
+        nl, n_ext, nnz = halo.n_local, self.n_ext, self.nnz
+        rows_of = torch.repeat_interleave(torch.arange(self.n, device=dev), A.indptr[1:] - A.indptr[:-1], output_size=nnz)
+        in_halo = A.indices >= nl
+        ghost_r, ghost_c = A.indices[in_halo], rows_of[in_halo]
+        order = torch.argsort(ghost_r * n_ext + ghost_c)
+        counts = torch.bincount(ghost_r - nl, minlength=halo.n_halo)
+        ptr_ext = torch.cat((A.indptr, nnz + torch.cumsum(counts, 0))).contiguous()
+        idx_ext = torch.cat((A.indices, ghost_c[order])).contiguous()
+        plan = _plan.get_plan(n_ext, n_ext, idx_ext, ptr_ext)
+        br = plan.spmv_block_rows()
+        if br == 0:
+            return
+        idx_n, ptr_n, itype = plan.csr()
+        t_indptr, t_indices, t_perm, _ = plan.transpose()
+        # Rows of the extended matrix are stored in global column order, which is not ascending in
+        # the [local | halo] numbering, so "pattern equals its transpose" is checked as sets: the
+        # entries sorted by (row, column) must coincide with the transposed structure, and the
+        # position of the mirror entry (c, i) of every stored entry (i, c) follows from that order.
+        rows_ext = torch.repeat_interleave(torch.arange(n_ext, device=dev), ptr_ext[1:] - ptr_ext[:-1],
+                                           output_size=int(idx_ext.numel()))
+        srt = torch.argsort(rows_ext * n_ext + idx_ext)
+        if not (torch.equal(t_indptr, ptr_n) and torch.equal(t_indices, idx_n[srt])):
+            return
+        perm = torch.empty_like(t_perm)
+        perm[srt] = t_perm
+        k = torch.nonzero(in_halo).flatten()
+        perm[k] = k.to(perm.dtype)
+        self.plan_ext = plan
+        self.idx, self.ptr, self.itype = idx_n, ptr_n, itype
+        self.br = br
+        self.perm_ext = perm
+        self.nnz_ext = int(idx_ext.numel())
+        self.g_ext = torch.zeros(n_ext, dtype=A.data.dtype, device=dev)
+        self.grad_A_ext = torch.empty(self.nnz_ext, dtype=A.data.dtype, device=dev)
+        self.grad_A = self.grad_A_ext[:nnz]
+        self.fused = True
+        self.launches_per_step = 3 + 2 + len(halo.peers_out)
 
     def _p(self, t, offset_elems=0):
         return self._c.c_void_p(t.data_ptr() + offset_elems * t.element_size())
 
-    def _stream(self):
-        return self._c.c_void_p(torch.cuda.current_stream().cuda_stream)
-
-    def _fwd_rows(self, a, b, ptr, idx, perm, vec, out, out_off, rows_total_cols, hint):
+    def _fwd_call(self, a, b, ptr, idx, perm, vec, out, cols, hint):
+        """Argument tuple of nb200_spgemv_forward restricted to rows [a, b) (None if empty)."""
         if b <= a:
+            return None
+        return [b - a, cols, int(idx.numel()), self._p(self.A.data), self._p(idx), self._p(ptr, a),
+                self._p(perm) if perm is not None else None, self._p(vec), self._p(out, a),
+                hint if a % 256 == 0 else 0, self._p(self.status), self.code, self.itype, None]
+
+    def _prepare(self, g):
+        """Everything that does not change from step to step: ctypes argument lists and the
+        point-to-point descriptors (the buffers they name are fixed)."""
+        halo, lib = self.A.halo, self._cabi.lib()
+        nl = halo.n_local
+        a, b = self.interior
+        self._g = g
+        self._lib = lib
+        self._pack = [[halo.send_counts[p], self._p(self.x_ext), self._p(halo.send[p]), self._p(self.send_bufs[p]),
+                       self.code, self._cabi.I64, None] for p in halo.peers_out]
+        self._fwd_ops = [dist.P2POp(dist.isend, self.send_bufs[p], halo._peer(p), group=halo.group) for p in halo.peers_out]
+        for p in halo.peers_in:
+            o = nl + halo.recv_offsets[p]
+            self._fwd_ops.append(dist.P2POp(dist.irecv, self.x_ext[o:o + halo.recv_counts[p]], halo._peer(p), group=halo.group))
+        fw = lambda lo, hi: self._fwd_call(lo, hi, self.ptr, self.idx, None, self.x_ext, self.y, self.n_ext, self.br)  # noqa: E731
+        self._fwd_interior = fw(a, b)
+        self._fwd_boundary = [c for c in (fw(0, a), fw(b, self.n)) if c is not None]
+        tp = lambda lo, hi: self._fwd_call(lo, hi, self.t_indptr, self.t_indices, self.t_perm, g, self.gx_ext, self.n, self.tbr)  # noqa: E731
+        self._t_halo = tp(nl, self.n_ext)
+        self._t_local = tp(0, nl)
+        self._bwd_ops = []
+        for p in halo.peers_in:
+            o = nl + halo.recv_offsets[p]
+            self._bwd_ops.append(dist.P2POp(dist.isend, self.gx_ext[o:o + halo.recv_counts[p]], halo._peer(p), group=halo.group))
+        for p in halo.peers_out:
+            self._bwd_ops.append(dist.P2POp(dist.irecv, self.recv_bufs[p], halo._peer(p), group=halo.group))
+        self._grad_A = [self.n, self.n_ext, self.nnz, self._p(self.idx), self._p(self.ptr), self._p(self.x_ext),
+                        self._p(g), self._p(self.grad_A), self.br, self._p(self.status), self.code, self.itype, None]
+        if self.fused:
+            def sym(lo, hi):
+                return [self.n_ext, self.nnz_ext, lo, hi, self._p(self.A.data), self._p(self.idx), self._p(self.ptr),
+                        self._p(self.perm_ext), self._p(self.x_ext), self._p(self.g_ext), self._p(self.grad_A_ext),
+                        self._p(self.gx_ext), self.br, self._p(self.status), self.code, self.itype, None]
+            self._sym_ghost = sym(nl, self.n_ext) if self.n_ext > nl else None
+            self._sym_local = sym(0, nl)
+
+    def _launch(self, fn, args, stream):
+        if args is None:
             return
-        self._cabi.call("nb200_spgemv_forward", b - a, rows_total_cols, self.nnz, self._p(self.A.data), self._p(idx),
-                        self._p(ptr, a), self._p(perm) if perm is not None else None, self._p(vec),
-                        self._p(out, out_off + a), hint if a % 256 == 0 else 0, self._p(self.status), self.code,
-                        self.itype, self._stream())
+        args[-1] = stream
+        rc = fn(*args)
+        if rc != 0:
+            raise self._cabi.NB200Error(fn.__name__, rc, self._lib.nb200_status_string(rc).decode())
 
     def forward(self):
         """y = A x with x taken from x_ext[:n_local]."""
-        halo = self.A.halo
-        ops = []
-        for p in halo.peers_out:
-            self._cabi.call("nb200_gather", halo.send_counts[p], self._p(self.x_ext), self._p(halo.send[p]),
-                            self._p(self.send_bufs[p]), self.code, self._cabi.I64, self._stream())
-            ops.append(dist.P2POp(dist.isend, self.send_bufs[p], halo._peer(p), group=halo.group))
-        for p in halo.peers_in:
-            o = halo.n_local + halo.recv_offsets[p]
-            ops.append(dist.P2POp(dist.irecv, self.x_ext[o:o + halo.recv_counts[p]], halo._peer(p), group=halo.group))
-        reqs = dist.batch_isend_irecv(ops) if ops else []
-        a, b = self.interior
-        self._fwd_rows(a, b, self.ptr, self.idx, None, self.x_ext, self.y, 0, self.n_ext, self.br)
+        if not hasattr(self, "_lib"):
+            self._prepare(torch.zeros(self.n, dtype=self.y.dtype, device=self.y.device))
+        lib = self._lib
+        stream = self._c.c_void_p(torch.cuda.current_stream().cuda_stream)
+        for args in self._pack:
+            self._launch(lib.nb200_gather, args, stream)
+        reqs = dist.batch_isend_irecv(self._fwd_ops) if self._fwd_ops else []
+        self._launch(lib.nb200_spgemv_forward, self._fwd_interior, stream)
         for r in reqs:
             r.wait()
-        self._fwd_rows(0, a, self.ptr, self.idx, None, self.x_ext, self.y, 0, self.n_ext, self.br)
-        self._fwd_rows(b, self.n, self.ptr, self.idx, None, self.x_ext, self.y, 0, self.n_ext, self.br)
+        for args in self._fwd_boundary:
+            self._launch(lib.nb200_spgemv_forward, args, stream)
         return self.y
 
     def backward(self, g):
         """grad_A (pattern of the local rows) and grad_x (local block) for upstream gradient g;
         x_ext must still hold the forward's values."""
-        halo = self.A.halo
-        nl = halo.n_local
+        if self.fused and g.data_ptr() != self.g_ext.data_ptr():
+            self.g_ext[:self.n].copy_(g)            # callers may also write into g_ext[:n] directly
+            g = self.g_ext[:self.n]
+        if not hasattr(self, "_lib") or self._g.data_ptr() != g.data_ptr():
+            self._prepare(g)
+        lib, halo = self._lib, self.A.halo
+        stream = self._c.c_void_p(torch.cuda.current_stream().cuda_stream)
         # partial sums for halo columns first, so that their exchange overlaps the rest
-        self._fwd_rows(nl, self.n_ext, self.t_indptr, self.t_indices, self.t_perm, g, self.gx_ext, 0, self.n, self.tbr)
-        ops = []
-        for p in halo.peers_in:
-            o = nl + halo.recv_offsets[p]
-            ops.append(dist.P2POp(dist.isend, self.gx_ext[o:o + halo.recv_counts[p]], halo._peer(p), group=halo.group))
-        for p in halo.peers_out:
-            ops.append(dist.P2POp(dist.irecv, self.recv_bufs[p], halo._peer(p), group=halo.group))
-        reqs = dist.batch_isend_irecv(ops) if ops else []
-        self._cabi.call("nb200_spgemv_grad_A", self.n, self.n_ext, self.nnz, self._p(self.idx), self._p(self.ptr),
-                        self._p(self.x_ext), self._p(g), self._p(self.grad_A), self.br, self._p(self.status),
-                        self.code, self.itype, self._stream())
-        self._fwd_rows(0, nl, self.t_indptr, self.t_indices, self.t_perm, g, self.gx_ext, 0, self.n, self.tbr)
+        if self.fused:
+            self._launch(lib.nb200_spgemv_backward_symmetric_rows, self._sym_ghost, stream)
+            reqs = dist.batch_isend_irecv(self._bwd_ops) if self._bwd_ops else []
+            self._launch(lib.nb200_spgemv_backward_symmetric_rows, self._sym_local, stream)
+        else:
+            self._launch(lib.nb200_spgemv_forward, self._t_halo, stream)
+            reqs = dist.batch_isend_irecv(self._bwd_ops) if self._bwd_ops else []
+            self._launch(lib.nb200_spgemv_grad_A, self._grad_A, stream)
+            self._launch(lib.nb200_spgemv_forward, self._t_local, stream)
         for r in reqs:
             r.wait()
         for p in halo.peers_out:
@@ -405,6 +495,9 @@ def bench_steps(n, rank, world, dev, ops):
     g = g_h.to(dev)
     engine = DistSpMVEngine(A)
     engine.x_ext[:rows_per] = x_h.to(dev)
+    if engine.fused:
+        engine.g_ext[:rows_per] = g
+        g = engine.g_ext[:rows_per]
     A.requires_grad = True
 
     def step_dev():
@@ -430,6 +523,6 @@ def bench_steps(n, rank, world, dev, ops):
     n_ext = A.halo.n_local + A.halo.n_halo
     info = {"nnz": int(d.numel()), "rows": rows_per, "cols": n_ext, "index_bytes": 4,
             "launches_per_step": engine.launches_per_step, "status_word": engine.status,
-            "kernels": "tma-pipelined" if engine.br else "register-staged",
+            "kernels": ("tma-pipelined, fused backward over ghost rows" if engine.fused else "tma-pipelined") if engine.br else "register-staged",
             "h2d_bytes": 2 * rows_per * 8, "d2h_bytes": (2 * rows_per + int(d.numel())) * 8, "roofline": None}
     return step_dev, step_e2e, info

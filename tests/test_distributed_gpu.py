@@ -21,7 +21,10 @@ def _worker(rank, world, init_file):
     from numml_b200 import distributed as nd, workloads as W
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", init_method="file://" + init_file, rank=rank, world_size=world, device_id=dev)
+    import datetime
+    # a short collective timeout: if one rank fails an assertion the other must not wait for long
+    dist.init_process_group("nccl", init_method="file://" + init_file, rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=90))
     try:
         d, i, p, (m, n) = W.poisson3d_7pt(12, torch.float64, nz=12 * world)
         bounds = nd.partition_rows(m, world)
@@ -40,6 +43,7 @@ def _worker(rank, world, init_file):
         assert torch.allclose(xl.grad.cpu(), gx_ref[lo:hi], rtol=1e-13, atol=1e-13)
         # the pre-planned engine (overlapped exchange, sub-range launches) gives the same results
         eng = nd.DistSpMVEngine(A)
+        assert eng.fused                      # symmetric stencil block: one-pass backward over ghost rows
         eng.x_ext[:hi - lo] = x[lo:hi].to(dev)
         for _ in range(2):
             y2 = eng.forward()
