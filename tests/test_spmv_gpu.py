@@ -182,3 +182,51 @@ def test_cpu_tensors_are_rejected(ops):
     d, i, p, (m, n) = W.poisson2d_5pt(4, torch.float32)
     with pytest.raises(RuntimeError, match="CUDA"):
         ops.spgemv_forward(m, n, d, i, p, torch.ones(n))
+
+
+def _cabi_ptr(t):
+    import ctypes
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def test_row_range_entry_points(oracle):
+    """The pieces the row-partitioned driver schedules by hand, called through the C ABI:
+    nb200_csr_block_profile, nb200_spgemv_grad_A and nb200_spgemv_backward_symmetric_rows on two
+    row ranges that together cover the matrix."""
+    import ctypes
+    from numml_b200 import _cabi, _plan
+    d, i, p, (m, k) = W.poisson3d_7pt(20, torch.float64)
+    d = W.randn(d.numel(), 9, torch.float64)
+    x, g = W.randn(k, 0, torch.float64), W.randn(m, 1, torch.float64)
+    gA_ref, gx_ref = oracle.spgemv_backward(g, m, k, d, i, p, x)
+    dd, di, dp, dx, dg = [t.cuda() for t in (d, i, p, x, g)]
+    plan = _plan.get_plan(m, k, di, dp)
+    idx, ptr, itype = plan.csr()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    prof = torch.empty(4, dtype=torch.int64, device="cuda")
+    _cabi.call("nb200_csr_block_profile", m, _cabi_ptr(ptr), itype, _cabi_ptr(prof), stream)
+    lens = (p[1:] - p[:-1])
+    expect = [int(torch.stack([lens[b:b + R].sum() for b in range(0, m, R)]).max()) for R in (256, 128, 64, 32)]
+    assert prof.tolist() == expect
+    assert _cabi.lib().nb200_spmv_pipeline_tile() >= expect[0]
+
+    for block_rows in (0, 256):
+        gA = torch.full_like(dd, float("nan"))
+        _cabi.call("nb200_spgemv_grad_A", m, k, d.numel(), _cabi_ptr(idx), _cabi_ptr(ptr), _cabi_ptr(dx), _cabi_ptr(dg),
+                   _cabi_ptr(gA), block_rows, _cabi_ptr(status), _cabi.F64, itype, stream)
+        assert_same(gA_ref, gA, f"grad_A (block_rows={block_rows})")
+
+    assert plan.pattern_symmetric()
+    _, _, t_perm, _ = plan.transpose()
+    gA = torch.full_like(dd, float("nan"))
+    gx = torch.full_like(dx, float("nan"))
+    cut = 4096                                  # two launches: rows [cut, m) first, then [0, cut)
+    for lo, hi in ((cut, m), (0, cut)):
+        _cabi.call("nb200_spgemv_backward_symmetric_rows", m, d.numel(), lo, hi, _cabi_ptr(dd), _cabi_ptr(idx),
+                   _cabi_ptr(ptr), _cabi_ptr(t_perm), _cabi_ptr(dx), _cabi_ptr(dg), _cabi_ptr(gA), _cabi_ptr(gx), 256,
+                   _cabi_ptr(status), _cabi.F64, itype, stream)
+    assert_same(gA_ref, gA, "grad_A (fused, two row ranges)")
+    assert_same(gx_ref, gx, "grad_x (fused, two row ranges)")
+    assert int(status.item()) == 0
