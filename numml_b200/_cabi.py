@@ -84,9 +84,14 @@ def lib():
     return _lib
 
 
+_functions = {}
+
+
 def call(name, *args):
     """Call an int-status entry point and raise NB200Error on failure."""
-    handle = lib()
-    status = getattr(handle, name)(*args)
+    fn = _functions.get(name)
+    if fn is None:
+        fn = _functions[name] = getattr(lib(), name)
+    status = fn(*args)
     if status != 0:
-        raise NB200Error(name, status, handle.nb200_status_string(status).decode())
+        raise NB200Error(name, status, lib().nb200_status_string(status).decode())

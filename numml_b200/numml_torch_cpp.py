@@ -66,7 +66,25 @@ def _ptr(t):
 
 
 def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
+
+
+class _NoGuard:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def _on(dev):
+    """Device guard that costs nothing when `dev` is already the current device."""
+    if dev.index is None or dev.index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(dev)
 
 
 _status_words = {}
@@ -89,7 +107,7 @@ def spgemv_forward(A_rows, A_cols, A_data, A_col_ind, A_rowptr, x):
     x = _values(x, A_data)
     plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_col_ind), _index_tensor(A_rowptr))
     idx, ptr, itype = plan.csr()
-    with torch.cuda.device(dev):
+    with _on(dev):
         block_rows = plan.spmv_block_rows() if spmv_kernel == "auto" else 0
         y = torch.empty(A_rows, dtype=A_data.dtype, device=dev)
         _cabi.call("nb200_spgemv_forward", A_rows, A_cols, plan.nnz, _ptr(A_data), _ptr(idx), _ptr(ptr),
@@ -110,7 +128,7 @@ def spgemv_backward(grad_z, A_rows, A_cols, A_data, A_col_ind, A_rowptr, x):
         t_indptr = t_indices = t_perm = None
     else:
         raise RuntimeError(f"unknown spmv_backward_mode {spmv_backward_mode!r}")
-    with torch.cuda.device(dev):
+    with _on(dev):
         auto = spmv_kernel == "auto"
         block_rows = plan.spmv_block_rows() if auto else 0
         t_block_rows = plan.spmv_block_rows(transposed=True) if (auto and t_indptr is not None) else 0
@@ -138,7 +156,7 @@ def csr_transpose_forward(A_rows, A_columns, A_data, A_indices, A_indptr):
     # the returned arrays are int64 like the reference's, produced directly at that width
     t_indptr, t_indices, t_perm = _plan.transpose_structure(A_rows, A_columns, A_indices, A_indptr,
                                                             _cabi.I64, _cabi.I64)
-    with torch.cuda.device(dev):
+    with _on(dev):
         At_data = torch.empty_like(A_data)
         _cabi.call("nb200_gather", nnz, _ptr(A_data), _ptr(t_perm), _ptr(At_data),
                    _dtype_code(A_data), _cabi.I64, _stream())
@@ -149,7 +167,7 @@ def csr_transpose_backward(grad_At, At_to_A_idx):
     dev = _require_cuda(grad_At, At_to_A_idx)
     grad_At = _values(grad_At)
     idx = _index_tensor(At_to_A_idx)
-    with torch.cuda.device(dev):
+    with _on(dev):
         grad_A = torch.empty_like(grad_At)
         _cabi.call("nb200_scatter", int(grad_At.numel()), _ptr(grad_At), _ptr(idx), _ptr(grad_A),
                    _dtype_code(grad_At), _cabi.I64, _stream())
@@ -174,7 +192,7 @@ def spdmm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B):
     plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
     idx, ptr, itype = plan.csr()
     K = int(B.shape[1])
-    with torch.cuda.device(dev):
+    with _on(dev):
         C = torch.empty((A_rows, K), dtype=A_data.dtype, device=dev)
         _cabi.call("nb200_spdmm_forward", A_rows, A_cols, K, plan.nnz, _ptr(A_data), _ptr(idx), _ptr(ptr), None,
                    _ptr(B), _ptr(C), _dtype_code(A_data), itype, _stream())
@@ -191,7 +209,7 @@ def spdmm_backward(A_rows, A_cols, A_data, A_indices, A_indptr, B, grad_C):
     t_indptr, t_indices, t_perm, _ = plan.transpose()
     K = int(B.shape[1])
     code = _dtype_code(A_data)
-    with torch.cuda.device(dev):
+    with _on(dev):
         grad_A = torch.empty_like(A_data)
         grad_B = torch.empty((A_cols, K), dtype=A_data.dtype, device=dev)
         _cabi.call("nb200_spdmm_backward_grad_A", A_rows, A_cols, K, plan.nnz, _ptr(idx), _ptr(ptr),
@@ -228,7 +246,7 @@ def spgemm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B_rows, B_cols, 
     ai, ap, bi, bp, itype = _common_width(plan_a, plan_b)
     code = _dtype_code(A_data)
     vbytes = A_data.element_size()
-    with torch.cuda.device(dev):
+    with _on(dev):
         wbytes = _cabi.lib().nb200_spgemm_workspace_bytes(A_rows)
         work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
         _cabi.call("nb200_spgemm_plan", A_rows, A_cols, plan_a.nnz, _ptr(ai), _ptr(ap), _ptr(bp), itype,
@@ -265,7 +283,7 @@ def spgemm_backward(grad_C, C_indices, C_indptr, A_rows, A_cols, A_data, A_indic
         t_indptr, t_indices, t_perm, _ = plan_a.transpose()
     else:
         t_indptr, t_indices, t_perm = _plan.transpose_structure(A_rows, A_cols, ai, ap, _cabi.I64, _cabi.I64)
-    with torch.cuda.device(dev):
+    with _on(dev):
         grad_A = torch.empty_like(A_data)
         grad_B = torch.empty_like(B_data)
         _cabi.call("nb200_spgemm_backward", A_rows, A_cols, plan_a.nnz, _ptr(A_data), _ptr(ai), _ptr(ap),
@@ -326,7 +344,7 @@ def sptrsv_forward(A_rows, A_cols, A_data, A_indices, A_indptr, lower, unit, b):
     b = _rhs(b, A_rows, A_data)
     plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
     idx, ptr, itype = plan.csr()
-    with torch.cuda.device(dev):
+    with _on(dev):
         order, _ = plan.sptrsv_order(lower)
         return _solve(plan, A_data, idx, ptr, None, itype, order, lower, unit, b)
 
@@ -339,7 +357,7 @@ def sptrsv_backward(grad_x, x, A_rows, A_cols, A_data, A_indices, A_indptr, lowe
     plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
     idx, ptr, itype = plan.csr()
     nrhs = 1 if x.ndim == 1 else int(x.shape[1])
-    with torch.cuda.device(dev):
+    with _on(dev):
         t_indptr, t_indices, t_perm, _ = plan.transpose()
         order_t, _ = plan.sptrsv_order(not lower, transposed=True)
         # grad_b = A^{-T} grad_x: the opposite-triangle solve on the transposed structure
