@@ -194,17 +194,17 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
     // Per block each thread needs the block's nonzero range (same for all threads) and, if it owns
     // a row of the block, that row's range (and g for kGradA).  They are fetched one block ahead so
     // that their latency is hidden behind the current block's work.
-    struct BlockInfo { int64_t begin, end, s, e; T g; };
+    struct BlockInfo { int64_t begin; int cnt, lo, hi; T g; };   // entries of the block; this thread's row, relative to begin
     auto fetch = [&](int64_t blk) {
         BlockInfo f{0, 0, 0, 0, (T)0};
         if (blk < a.num_blocks) {
             const int64_t r0 = a.row0 + blk * a.block_rows, r1 = min(r0 + (int64_t)a.block_rows, a.rows);
             f.begin = (int64_t)a.indptr[r0];
-            f.end = (int64_t)a.indptr[r1];
+            f.cnt = (int)min((int64_t)a.indptr[r1] - f.begin, (int64_t)0x3fffffff);
             const int64_t r = r0 + tid;
             if (tid < a.block_rows && r < r1) {
-                f.s = (int64_t)a.indptr[r];
-                f.e = (int64_t)a.indptr[r + 1];
+                f.lo = (int)min((int64_t)a.indptr[r] - f.begin, (int64_t)0x3fffffff);
+                f.hi = (int)min((int64_t)a.indptr[r + 1] - f.begin, (int64_t)0x3fffffff);
                 if (MODE == kGradA || MODE == kBackwardSym) f.g = a.rowvec[r];
             }
         }
@@ -219,11 +219,12 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
         const BlockInfo nxt = fetch(b + gridDim.x);
 
         const int64_t r0 = a.row0 + b * a.block_rows, r1 = min(r0 + (int64_t)a.block_rows, a.rows);
-        const int64_t begin = cur.begin, end = cur.end;
+        const int64_t begin = cur.begin, end = cur.begin + cur.cnt;
         const int64_t base = begin & ~(int64_t)3;
+        const int shift = (int)(begin - base);                       // stage offset of the block's first entry
         const int64_t bulk_stop = min(min((end + 3) & ~(int64_t)3, nnz_bulk_end), base + kPipeTile);
         const bool owns_row = tid < a.block_rows && r0 + tid < r1;
-        const int64_t stage_end = min(bulk_stop, base + kPipeTile);   // entries below this are in the stage
+        const int staged_cnt = (int)max(bulk_stop - base, (int64_t)0);   // stage offsets below this hold data
 
         if (!mbar_wait(full + s, ph)) {
             if (a.status && tid == 0) atomicExch(a.status, (int)NB200_ERR_WAIT_BUDGET);
@@ -233,24 +234,32 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
         const T* sval = reinterpret_cast<const T*>(stage_A(s));     // kForward
         const I* sperm = reinterpret_cast<const I*>(stage_A(s));    // kForwardPerm, kBackwardSym
         T* sout = reinterpret_cast<T*>(stage_P(s));                 // kGradA, kBackwardSym
+        T* const outp = a.out + base;                                // entry with stage offset o is out[base + o]
 
         // ---- one thread per row: entries from the stage, x through L1/L2, storage order ----
         if (owns_row) {
             T acc = 0;
-            for (int64_t k0 = cur.s; k0 < cur.e; k0 += CH) {
-                const int n = (int)min((int64_t)CH, cur.e - k0);
+            const int o_lo = cur.lo + shift, o_hi = cur.hi + shift;
+            const bool all_staged = o_hi <= staged_cnt;              // false only at the ragged end of the arrays
+            for (int o0 = o_lo; o0 < o_hi; o0 += CH) {
+                const int n = min(CH, o_hi - o0);
                 I c[CH];
                 T v[CH], xv[CH];
 #pragma unroll
                 for (int j = 0; j < CH; ++j) {
                     c[j] = 0; v[j] = 0;
                     if (j < n) {
-                        const int64_t k = k0 + j;
-                        const bool staged = k < stage_end;
-                        c[j] = staged ? sidx[k - base] : a.indices[k];
-                        if (MODE == kForward) v[j] = staged ? sval[k - base] : a.data[k];
-                        if (MODE == kForwardPerm || MODE == kBackwardSym)
-                            v[j] = ldg(a.data + (staged ? sperm[k - base] : a.perm[k]));
+                        const int o = o0 + j;
+                        if (all_staged || o < staged_cnt) {
+                            c[j] = sidx[o];
+                            if (MODE == kForward) v[j] = sval[o];
+                            if (MODE == kForwardPerm || MODE == kBackwardSym) v[j] = ldg(a.data + sperm[o]);
+                        } else {
+                            const int64_t k = base + o;
+                            c[j] = a.indices[k];
+                            if (MODE == kForward) v[j] = a.data[k];
+                            if (MODE == kForwardPerm || MODE == kBackwardSym) v[j] = ldg(a.data + a.perm[k]);
+                        }
                     }
                 }
 #pragma unroll
@@ -264,9 +273,9 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
 #pragma unroll
                     for (int j = 0; j < CH; ++j) {
                         if (j < n) {
-                            const int64_t k = k0 + j;
-                            const T o = mul_rn(cur.g, xv[j]);
-                            if (!DIRECT && k < base + kPipeTile) sout[k - base] = o; else a.out[k] = o;
+                            const int o = o0 + j;
+                            const T val = mul_rn(cur.g, xv[j]);
+                            if (!DIRECT && o < kPipeTile) sout[o] = val; else outp[o] = val;
                             acc = add_rn(acc, mul_rn(gv[j], v[j]));
                         }
                     }
@@ -274,9 +283,9 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
 #pragma unroll
                     for (int j = 0; j < CH; ++j) {
                         if (j < n) {
-                            const int64_t k = k0 + j;
-                            const T o = mul_rn(cur.g, xv[j]);
-                            if (k < base + kPipeTile) sout[k - base] = o; else a.out[k] = o;
+                            const int o = o0 + j;
+                            const T val = mul_rn(cur.g, xv[j]);
+                            if (o < kPipeTile) sout[o] = val; else outp[o] = val;
                         }
                     }
                 } else {
@@ -339,7 +348,7 @@ template <typename T, typename I>
 int spmv_pipe_forward(int64_t rows, int64_t nnz, int block_rows, const T* data, const I* indices, const I* indptr,
                       const I* perm, const T* x, T* y, int32_t* status, cudaStream_t st) {
     PipeArgs<T, I> a{0, rows, nnz, ceil_div(rows, (int64_t)block_rows), block_rows, data, indices, indptr, perm, x, nullptr, y, nullptr, status};
-    if (perm) return spmv_pipe_launch<T, I, kForwardPerm, 3>(a, st);
+    if (perm) return spmv_pipe_launch<T, I, kForwardPerm, 2, 4, 4>(a, st);
     // two stages, four entries per gather round, four CTAs per SM: measured 43 us on the 128^3 Poisson
     // matrix against 48 us for three stages / eight entries / three CTAs -- occupancy beats pipeline depth
     return spmv_pipe_launch<T, I, kForward, 2, 4, 4>(a, st);
@@ -349,7 +358,7 @@ template <typename T, typename I>
 int spmv_pipe_grad_A(int64_t rows, int64_t nnz, int block_rows, const I* indices, const I* indptr, const T* x,
                      const T* g, T* grad_A, int32_t* status, cudaStream_t st) {
     PipeArgs<T, I> a{0, rows, nnz, ceil_div(rows, (int64_t)block_rows), block_rows, nullptr, indices, indptr, nullptr, x, g, grad_A, nullptr, status};
-    return spmv_pipe_launch<T, I, kGradA, 3>(a, st);
+    return spmv_pipe_launch<T, I, kGradA, 2, 4, 4>(a, st);
 }
 
 template <typename T, typename I>
@@ -361,7 +370,10 @@ int spmv_pipe_backward_sym(int64_t row_begin, int64_t row_end, int64_t nnz, int 
     // four stages, four entries per gather round, grad_A written straight from the row threads:
     // the best of the measured variants (staged + coalesced grad_A stores cost a third of the
     // shared memory and with it the pipeline depth)
-    return spmv_pipe_launch<T, I, kBackwardSym, 4, 4, 3, true>(a, st);
+    // Measured on the 128^3 Poisson matrix (us): 2 stages / 2 entries per gather round / 4 CTAs per SM 94.5;
+    // 2/4/4 98; 4/4/3 104; 3/8/3 112; anything that needs 5+ CTAs per SM spills and is slower; staging
+    // grad_A in shared memory for coalesced stores costs more occupancy than it saves (107).
+    return spmv_pipe_launch<T, I, kBackwardSym, 2, 2, 4, true>(a, st);
 }
 
 #define NB200_INSTANTIATE_PIPE(T, I)                                                                                 \
