@@ -222,7 +222,9 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a bounded collective timeout: a rank that fails must not leave the others waiting for long
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
 
     from numml_b200 import numml_torch_cpp as ops
     if args.backward:
@@ -303,7 +305,7 @@ def run(args, rank, world, dev, dist, n, peak, peak_kind):
         "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f64", "data": "synthetic",
         "config": {"workload": f"poisson3d_7pt_{n}^3_per_gpu_fp64_spmv_fwd_bwd", "rows_per_gpu": m, "nnz_per_gpu": nnz,
-                   "index_bytes": w, "backward": ops.spmv_backward_mode, "kernels": info.get("kernels"),
+                   "index_bytes": w, "backward": ops.spmv_backward_mode, "kernels": info.get("kernels"), "schedule": info.get("schedule", "eager launches"),
                    "partition": "z-slabs, one halo plane per neighbour" if world > 1 else "single GPU",
                    "l2": "working set per step (>= 350 MB) is larger than the 126 MB L2; no explicit flush"},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / e2e_steps,

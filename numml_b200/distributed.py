@@ -20,6 +20,9 @@ the local compute goes through an operator module with the reference's function 
 ranks with a CPU implementation of the same functions injected by the tests.
 The triangular solve does not shard (its dependency chain spans the matrix).
 """
+import os
+import sys
+
 import torch
 import torch.distributed as dist
 
@@ -455,6 +458,28 @@ class DistSpMVEngine:
             self._launch(lib.nb200_spgemv_forward, args, stream)
         return self.y
 
+    def capture(self, g, warmup=3):
+        """Record forward() + backward(g) -- kernels, packs and the NCCL exchanges -- into one CUDA
+        graph and return a function that replays it.  The launch schedule is identical on every
+        step, so replaying removes the per-step host work (a dozen launches and two grouped
+        point-to-point calls), which at two or more GPUs is as long as the GPU work itself.
+        Every rank must call this at the same point.  Warm-up steps run first on a side stream, as
+        graph capture requires."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self.forward()
+                self.backward(g)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.forward()
+            self.backward(g)
+        self._graph = graph
+        return graph.replay
+
     def backward(self, g):
         """grad_A (pattern of the local rows) and grad_x (local block) for upstream gradient g;
         x_ext must still hold the forward's values."""
@@ -500,9 +525,17 @@ def bench_steps(n, rank, world, dev, ops):
         g = engine.g_ext[:rows_per]
     A.requires_grad = True
 
-    def step_dev():
+    def step_eager():
         engine.forward()
         engine.backward(g)
+
+    step_dev, mode = step_eager, "eager launches"
+    if os.environ.get("NB200_BENCH_GRAPH", "1") == "1":
+        try:
+            step_dev, mode = engine.capture(g), "one CUDA graph per step (kernels + NCCL exchanges)"
+        except Exception as e:          # capture is an optimisation; the eager schedule is always valid
+            print(f"rank {rank}: CUDA graph capture failed ({type(e).__name__}: {e}); running eager launches", file=sys.stderr)
+            step_dev = step_eager
 
     x_pin, g_pin = x_h.pin_memory(), g_h.pin_memory()
     y_pin = torch.empty(rows_per, dtype=torch.float64).pin_memory()
@@ -522,7 +555,7 @@ def bench_steps(n, rank, world, dev, ops):
 
     n_ext = A.halo.n_local + A.halo.n_halo
     info = {"nnz": int(d.numel()), "rows": rows_per, "cols": n_ext, "index_bytes": 4,
-            "launches_per_step": engine.launches_per_step, "status_word": engine.status,
+            "launches_per_step": engine.launches_per_step, "status_word": engine.status, "schedule": mode,
             "kernels": ("tma-pipelined, fused backward over ghost rows" if engine.fused else "tma-pipelined") if engine.br else "register-staged",
             "h2d_bytes": 2 * rows_per * 8, "d2h_bytes": (2 * rows_per + int(d.numel())) * 8, "roofline": None}
     return step_dev, step_e2e, info
