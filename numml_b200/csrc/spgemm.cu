@@ -8,8 +8,10 @@
 //     bin 2: 256 threads per row, 8192-slot (symbolic) / 4096-slot (numeric) table in shared memory
 //     bin 3: 256 threads per row, table in a caller-provided global-memory spill area
 // Column keys are inserted with atomicCAS and linear probing (load factor <= 1/2); the numeric
-// phase accumulates values with shared/global atomics, then sorts the whole table by key with a
-// bitonic network (empty slots sort last) and writes the first nnz entries.  The pattern is
+// phase accumulates values with shared/global atomics and then emits the row in ascending column
+// order: 64-slot tables by counting, for every occupied slot, the smaller keys in the table (its
+// position in the sorted row), larger tables by a bitonic sort of the whole table (empty slots
+// sort last) followed by a copy of the first nnz entries.  The pattern is
 // purely structural: a product that cancels numerically still yields a stored zero, as in the
 // reference.
 //

@@ -285,6 +285,55 @@ def dist_spgemm(A, B):
                                 n_ext, B.global_shape[1], ext_data, ext_indices, ext_indptr)
 
 
+def ghost_row_extension(indices, indptr, n_local, n_ext):
+    """Square, pattern-symmetric extension of a rank's block of rows.
+
+    ``indices`` / ``indptr`` describe n_local rows over n_ext = n_local + n_halo columns in
+    ``[local | halo]`` numbering.  One ghost row is appended per halo column, holding the mirror
+    images (c, i) of the halo entries (i, c), sorted by i.  Returns
+    ``(idx_ext, ptr_ext, in_halo)``: the extended CSR structure over n_ext rows and the mask of the
+    original entries that lie in halo columns.  Ghost entries carry no values of their own: in the
+    one-pass backward kernel a ghost row reads the values of the local entries it mirrors, which
+    makes its row sum exactly the partial sum of grad_x owed to the neighbour that owns the column;
+    a local entry in a halo column is paired with itself and multiplied by the zero that the
+    extended upstream gradient holds in ghost rows.
+    """
+    dev = indices.device
+    nnz = int(indices.numel())
+    rows_of = torch.repeat_interleave(torch.arange(n_local, device=dev), indptr[1:] - indptr[:-1], output_size=nnz)
+    in_halo = indices >= n_local
+    ghost_r, ghost_c = indices[in_halo], rows_of[in_halo]
+    order = torch.argsort(ghost_r * n_ext + ghost_c)
+    counts = torch.bincount(ghost_r - n_local, minlength=n_ext - n_local)
+    ptr_ext = torch.cat((indptr, nnz + torch.cumsum(counts, 0))).contiguous()
+    idx_ext = torch.cat((indices, ghost_c[order])).contiguous()
+    return idx_ext, ptr_ext, in_halo
+
+
+def mirror_positions(idx_ext, ptr_ext, in_halo, t_indptr, t_indices, t_perm):
+    """For every entry (i, c) of the extended structure, the storage position of its mirror (c, i),
+    or None if the pattern is not symmetric.
+
+    Rows of the extended matrix are stored in global column order, which is not ascending in the
+    [local | halo] numbering, so symmetry is checked on sets: the entries sorted by (row, column)
+    must coincide with the transposed structure ``(t_indptr, t_indices)``, whose ``t_perm`` then
+    gives the mirror of the q-th sorted entry.  Local entries in halo columns are mapped to
+    themselves (their mirror is a ghost entry without a value).
+    """
+    n_ext = int(ptr_ext.numel()) - 1
+    dev = idx_ext.device
+    rows_ext = torch.repeat_interleave(torch.arange(n_ext, device=dev), ptr_ext[1:] - ptr_ext[:-1],
+                                       output_size=int(idx_ext.numel()))
+    srt = torch.argsort(rows_ext * n_ext + idx_ext)
+    if not (torch.equal(t_indptr.to(ptr_ext.dtype), ptr_ext) and torch.equal(t_indices.to(idx_ext.dtype), idx_ext[srt])):
+        return None
+    perm = torch.empty_like(t_perm)
+    perm[srt] = t_perm
+    k = torch.nonzero(in_halo).flatten()
+    perm[k] = k.to(perm.dtype)
+    return perm
+
+
 class DistSpMVEngine:
     """Forward + backward of a row-partitioned SpMV as a fixed schedule of C-ABI launches over
     preallocated buffers, with the halo exchange overlapped with the rows that do not need it.
@@ -340,42 +389,21 @@ class DistSpMVEngine:
             self._build_symmetric_extension(_plan)
 
     def _build_symmetric_extension(self, _plan):
-        """Make the local block square and pattern-symmetric by appending one ghost row per halo
-        column holding the transposed halo entries.  The one-pass backward kernel then produces,
-        from the ghost rows, exactly the partial sums of grad_x that belong to the neighbours, and
-        from the local rows grad_A and the local part of grad_x.  Ghost entries carry no values:
-        a ghost row reads the values of the local entries it mirrors through the permutation, and
-        a local entry in a halo column is paired with itself and multiplied by the zero that the
-        extended upstream gradient holds there."""
+        """Switch the backward to the one-pass kernel on the ghost-row extension of the local block
+        (see ``ghost_row_extension``), if the block's pattern allows it."""
         A, halo = self.A, self.A.halo
         dev = A.data.device
         nl, n_ext, nnz = halo.n_local, self.n_ext, self.nnz
-        rows_of = torch.repeat_interleave(torch.arange(self.n, device=dev), A.indptr[1:] - A.indptr[:-1], output_size=nnz)
-        in_halo = A.indices >= nl
-        ghost_r, ghost_c = A.indices[in_halo], rows_of[in_halo]
-        order = torch.argsort(ghost_r * n_ext + ghost_c)
-        counts = torch.bincount(ghost_r - nl, minlength=halo.n_halo)
-        ptr_ext = torch.cat((A.indptr, nnz + torch.cumsum(counts, 0))).contiguous()
-        idx_ext = torch.cat((A.indices, ghost_c[order])).contiguous()
+        idx_ext, ptr_ext, in_halo = ghost_row_extension(A.indices, A.indptr, nl, n_ext)
         plan = _plan.get_plan(n_ext, n_ext, idx_ext, ptr_ext)
         br = plan.spmv_block_rows()
         if br == 0:
             return
         idx_n, ptr_n, itype = plan.csr()
         t_indptr, t_indices, t_perm, _ = plan.transpose()
-        # Rows of the extended matrix are stored in global column order, which is not ascending in
-        # the [local | halo] numbering, so "pattern equals its transpose" is checked as sets: the
-        # entries sorted by (row, column) must coincide with the transposed structure, and the
-        # position of the mirror entry (c, i) of every stored entry (i, c) follows from that order.
-        rows_ext = torch.repeat_interleave(torch.arange(n_ext, device=dev), ptr_ext[1:] - ptr_ext[:-1],
-                                           output_size=int(idx_ext.numel()))
-        srt = torch.argsort(rows_ext * n_ext + idx_ext)
-        if not (torch.equal(t_indptr, ptr_n) and torch.equal(t_indices, idx_n[srt])):
+        perm = mirror_positions(idx_ext, ptr_ext, in_halo, t_indptr, t_indices, t_perm)
+        if perm is None:
             return
-        perm = torch.empty_like(t_perm)
-        perm[srt] = t_perm
-        k = torch.nonzero(in_halo).flatten()
-        perm[k] = k.to(perm.dtype)
         self.plan_ext = plan
         self.idx, self.ptr, self.itype = idx_n, ptr_n, itype
         self.br = br

@@ -110,3 +110,58 @@ def test_partition_rows():
     b = nd.partition_rows(6, 2, indptr=indptr)
     assert b[0] == 0 and b[-1] == 6 and b == sorted(b)
     assert abs(int(indptr[b[1]]) - 100) <= 3
+
+
+def test_ghost_row_extension_reproduces_the_backward():
+    """The index logic behind the one-pass distributed backward, emulated on CPU: for each of two
+    row blocks of a 3-D stencil, build the ghost-row extension and the mirror positions (transposed
+    structure from the oracle), evaluate the kernel's formulas with plain loops and check that
+    grad_A and the exchanged grad_x equal the single-partition oracle."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import csr_oracle as oracle
+    from numml_b200 import distributed as nd, workloads as W
+    d, i, p, (m, n) = W.poisson3d_7pt(5, torch.float64, nz=10)
+    d = W.randn(d.numel(), 3, torch.float64)
+    x, g = W.randn(n, 1, torch.float64), W.randn(m, 2, torch.float64)
+    gA_ref, gx_ref = oracle.spgemv_backward(g, m, n, d, i, p, x)
+    bounds = [0, m // 2, m]
+    parts = []
+    for rank in range(2):
+        lo, hi = bounds[rank], bounds[rank + 1]
+        sl = slice(int(p[lo]), int(p[hi]))
+        data, gi, ptr = d[sl], i[sl], p[lo:hi + 1] - p[lo]
+        remote = (gi < lo) | (gi >= hi)
+        needed = torch.unique(gi[remote])
+        nl = hi - lo
+        n_ext = nl + needed.numel()
+        idx = torch.where(remote, nl + torch.searchsorted(needed, gi), gi - lo)
+        idx_ext, ptr_ext, in_halo = nd.ghost_row_extension(idx, ptr, nl, n_ext)
+        assert ptr_ext.numel() == n_ext + 1 and int(ptr_ext[-1]) == idx_ext.numel()
+        _, t_idx, t_ptr, t_perm = oracle.csr_transpose_forward(n_ext, n_ext, torch.zeros(idx_ext.numel(), dtype=torch.float64), idx_ext, ptr_ext)
+        perm = nd.mirror_positions(idx_ext, ptr_ext, in_halo, t_ptr, t_idx, t_perm)
+        assert perm is not None                         # the stencil block is pattern-symmetric
+        x_ext = torch.cat((x[lo:hi], x[needed]))
+        g_ext = torch.cat((g[lo:hi], torch.zeros(needed.numel(), dtype=torch.float64)))
+        gA = torch.zeros(idx_ext.numel(), dtype=torch.float64)
+        gx = torch.zeros(n_ext, dtype=torch.float64)
+        for r in range(n_ext):                          # what spmv_pipe_kernel mode 3 computes per row
+            acc = 0.0
+            for k in range(int(ptr_ext[r]), int(ptr_ext[r + 1])):
+                c = int(idx_ext[k])
+                gA[k] = g_ext[r] * x_ext[c]
+                acc += data[int(perm[k])] * g_ext[c]
+            gx[r] = acc
+        assert torch.equal(gA[:data.numel()], gA_ref[sl])
+        parts.append((lo, hi, needed, gx))
+    for rank in range(2):
+        lo, hi, _, gx = parts[rank]
+        total = gx[:hi - lo].clone()
+        olo, ohi, oneeded, ogx = parts[1 - rank]
+        sel = (oneeded >= lo) & (oneeded < hi)
+        total.index_add_(0, oneeded[sel] - lo, ogx[ohi - olo:][sel])
+        assert torch.allclose(total, gx_ref[lo:hi], rtol=1e-13, atol=1e-13)
+
+    # a block whose pattern is not symmetric is refused
+    idx, ptr = torch.tensor([1, 1]), torch.tensor([0, 1, 2])          # entries (0,1) and (1,1): (1,0) is missing
+    _, t_idx, t_ptr, t_perm = oracle.csr_transpose_forward(2, 2, torch.zeros(2, dtype=torch.float64), idx, ptr)
+    assert nd.mirror_positions(idx, ptr, torch.zeros(2, dtype=torch.bool), t_ptr, t_idx, t_perm) is None
