@@ -309,6 +309,23 @@ NB200_API int nb200_sptrsv_solve_f32_noalloc(int64_t n, int64_t nnz, int64_t nrh
                                              const float* b, float* x, int32_t* status,
                                              int64_t wait_budget_cycles, int itype, nb200_stream stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Conjugate gradients with a fixed iteration count.  Replaces the loop of conjugate_gradient
+ * (reference numml/krylov.py:83-155) for the case the benchmark configuration uses: no
+ * preconditioner, rtol = 0 and a given number of iterations, i.e. a stopping rule that can never
+ * fire.  The whole solve is enqueued on `stream` without a host round trip: per iteration one SpMV
+ * (nb200_spgemv_forward with `block_rows` as described there) and three fused vector kernels; the
+ * scalars alpha and beta stay in device memory.  On return (asynchronously) `x` holds the iterate
+ * and residual_history[0..iterations] the residual norms before the first and after every iteration.
+ * `has_x0` != 0: `x` holds the initial guess on entry; otherwise it is set to zero.
+ * `workspace` must hold nb200_cg_workspace_bytes(n, dtype) bytes.
+ * ------------------------------------------------------------------------------------------- */
+NB200_API size_t nb200_cg_workspace_bytes(int64_t n, int dtype);
+NB200_API int nb200_cg_fixed_iterations(int64_t n, int64_t nnz, const void* data, const void* indices, const void* indptr,
+                                        int block_rows, const void* b, void* x, int has_x0, void* residual_history,
+                                        int64_t iterations, void* workspace, size_t workspace_bytes, int32_t* status,
+                                        int dtype, int itype, nb200_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

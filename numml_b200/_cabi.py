@@ -47,6 +47,9 @@ SIGNATURES = {
     "nb200_sptrsv_solve_f32_noalloc_capacity": (_i64, []),
     "nb200_sptrsv_solve_f32_noalloc": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp, _vp, _vp, _i64,
                                               _int, _vp]),
+    "nb200_cg_workspace_bytes": (_sz, [_i64, _int]),
+    "nb200_cg_fixed_iterations": (_int, [_i64, _i64, _vp, _vp, _vp, _int, _vp, _vp, _int, _vp, _i64, _vp, _sz, _vp,
+                                         _int, _int, _vp]),
     "nb200_masked_outer": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _c.c_double, _vp, _int, _int, _vp]),
     "nb200_spdmm_backward_grad_A": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
 }

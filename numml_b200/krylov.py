@@ -54,6 +54,14 @@ def _cg_fixed_iterations(A, b, x, iterations):
     iteration as the tolerance test and the NaN check of the general loop do.  A NaN residual
     simply propagates to the end, where the history is cut at its first occurrence like the
     early return of the general loop."""
+    needs_autograd = torch.is_grad_enabled() and (getattr(A, "requires_grad", False) or b.requires_grad
+                                                  or (x is not None and x.requires_grad))
+    if isinstance(A, sp.SparseCSRTensor) and not needs_autograd:
+        # the whole loop runs inside the library: one SpMV and three fused vector kernels per
+        # iteration, scalars kept on the device
+        from . import numml_torch_cpp
+        x, hist = numml_torch_cpp.cg_fixed_iterations(A.shape[0], A.data.detach(), A.indices, A.indptr, b, x, iterations)
+        return x, _cut_at_nan(hist)
     if x is None:
         x = torch.zeros(A.shape[1], device=b.device, dtype=b.dtype)
         r = b.clone()
@@ -72,7 +80,9 @@ def _cg_fixed_iterations(A, b, x, iterations):
         p = r + (rz_new / rz) * p
         rz = rz_new
         hist[it + 1] = torch.sqrt(rz)
+    return x, _cut_at_nan(hist)
+
+
+def _cut_at_nan(hist):
     bad = torch.nonzero(torch.isnan(hist)).flatten()
-    if bad.numel() > 0:
-        hist = hist[:int(bad[0])]
-    return x, hist
+    return hist[:int(bad[0])] if bad.numel() > 0 else hist

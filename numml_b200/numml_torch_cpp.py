@@ -366,3 +366,29 @@ def sptrsv_backward(grad_x, x, A_rows, A_cols, A_data, A_indices, A_indptr, lowe
         _cabi.call("nb200_masked_outer", A_rows, plan.nnz, nrhs, _ptr(idx), _ptr(ptr), _ptr(grad_b), _ptr(x), -1.0,
                    _ptr(grad_A), _dtype_code(A_data), itype, _stream())
     return [grad_A, grad_b]
+
+
+# -------------------------------------------------------------------------------------------------
+# Conjugate gradients, fixed iteration count          reference numml/krylov.py:83-155
+# -------------------------------------------------------------------------------------------------
+def cg_fixed_iterations(A_rows, A_data, A_indices, A_indptr, b, x0, iterations):
+    """``iterations`` unpreconditioned CG steps for the square matrix A, enqueued without any host
+    synchronisation.  Returns ``(x, residual_history)``, the history having iterations + 1 entries."""
+    dev = _require_cuda(A_data, A_indices, A_indptr, b)
+    A_data = _values(A_data)
+    b = _values(b, A_data)
+    if b.ndim != 1 or b.shape[0] != A_rows:
+        raise RuntimeError(f"right-hand side must have shape ({A_rows},), got {tuple(b.shape)}")
+    plan = _plan.get_plan(A_rows, A_rows, _index_tensor(A_indices), _index_tensor(A_indptr))
+    idx, ptr, itype = plan.csr()
+    code = _dtype_code(A_data)
+    with _on(dev):
+        block_rows = plan.spmv_block_rows() if spmv_kernel == "auto" else 0
+        x = _values(x0, A_data).clone() if x0 is not None else torch.empty_like(b)
+        hist = torch.empty(iterations + 1, dtype=b.dtype, device=dev)
+        wbytes = _cabi.lib().nb200_cg_workspace_bytes(A_rows, code)
+        work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+        _cabi.call("nb200_cg_fixed_iterations", A_rows, plan.nnz, _ptr(A_data), _ptr(idx), _ptr(ptr), block_rows,
+                   _ptr(b), _ptr(x), int(x0 is not None), _ptr(hist), int(iterations), _ptr(work), wbytes,
+                   _ptr(_status_word(dev)), code, itype, _stream())
+    return x, hist

@@ -251,3 +251,39 @@ def test_golden_galerkin_autograd(sp, golden_api):
     assert_close(torch.from_numpy(golden_api["galerkin/AH_data"]), AH.data, "data")
     assert_close(torch.from_numpy(golden_api["galerkin/grad_A"]), A.data.grad, "grad_A")
     assert_close(torch.from_numpy(golden_api["galerkin/grad_P"]), P.data.grad, "grad_P")
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float64, 1e-9), (torch.float32, 2e-3)])
+@pytest.mark.parametrize("with_x0", [False, True])
+def test_library_cg_loop_vs_oracle(sp, oracle, dtype, tol, with_x0):
+    """The in-library CG loop (one SpMV + three fused vector kernels per iteration, scalars on the
+    device) against the same recurrence evaluated on CPU with the oracle SpMV."""
+    import numml_b200.krylov as kry
+    d, i, p, (m, n) = W.poisson3d_7pt(12, dtype)
+    b = W.randn(m, 3, dtype)
+    x0 = W.randn(m, 4, dtype) * 0.1 if with_x0 else None
+    iters = 20
+    x = torch.zeros(m, dtype=dtype) if x0 is None else x0.clone()
+    r = b.clone() if x0 is None else b - oracle.spgemv_forward(m, n, d, i, p, x0)
+    pv, rz = r.clone(), r @ r
+    hist = [rz.sqrt()]
+    for _ in range(iters):
+        Ap = oracle.spgemv_forward(m, n, d, i, p, pv)
+        alpha = rz / (Ap @ pv)
+        x = x + alpha * pv
+        r = r - alpha * Ap
+        rz_new = r @ r
+        pv = r + (rz_new / rz) * pv
+        rz = rz_new
+        hist.append(rz.sqrt())
+    A = sp.SparseCSRTensor((d, i, p), (m, n)).to(gpu)
+    xg, hg = kry.conjugate_gradient(A, b.to(gpu), x=None if x0 is None else x0.to(gpu), rtol=0.0, iterations=iters)
+    assert hg.numel() == iters + 1
+    assert_close(x, xg, "x", tol=tol)
+    assert_close(torch.stack(hist), hg, "residual history", tol=tol)
+    # the differentiable torch-op loop (taken when gradients are requested) agrees with it
+    Ag = A.copy()
+    Ag.requires_grad = True
+    xt, ht = kry.conjugate_gradient(Ag, b.to(gpu), x=None if x0 is None else x0.to(gpu), rtol=0.0, iterations=iters)
+    assert_close(xg, xt.detach(), "x (torch-op loop)", tol=tol)
+    assert xt.requires_grad
