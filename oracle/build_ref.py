@@ -12,6 +12,8 @@ clashes with this package's own operator module.  Output goes to ``oracle/_ref/`
 reference source is copied.
 
 Usage:  python oracle/build_ref.py [--reference /path/to/reference] [--force]
+The reference checkout is looked for at --reference, else at $NUMML_REFERENCE, else at the
+default location of the build machine.
 """
 import argparse
 import os
@@ -22,13 +24,14 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 MODULE = "numml_ref_cpp"
+DEFAULT_REFERENCE = os.environ.get("NUMML_REFERENCE", os.path.join(os.sep, "root", "reference"))
 
 
 def ref_module_path():
     return os.path.join(OUT_DIR, MODULE + sysconfig.get_config_var("EXT_SUFFIX"))
 
 
-def build(reference="/root/reference", force=False, verbose=True):
+def build(reference=DEFAULT_REFERENCE, force=False, verbose=True):
     """Compile the reference CPU extension into ``oracle/_ref``.  Returns the .so path, or None
     when the reference sources are not present (e.g. on a machine that only has prebuilt files)."""
     out = ref_module_path()
@@ -86,7 +89,7 @@ def load():
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=DEFAULT_REFERENCE)
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     p = build(a.reference, a.force)

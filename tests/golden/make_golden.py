@@ -1,12 +1,12 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE itself.
 
-Needs the reference checkout (default /root/reference) and its CPU operator module compiled
+Needs the reference checkout (--reference, else $NUMML_REFERENCE) and its CPU operator module compiled
 unmodified by oracle/build_ref.py.  Operator-level cases call the reference's C++ functions
 directly; API-level cases (autograd through SparseCSRTensor, conjugate gradients) import the
 reference's Python package on top of that module.  The outputs are small .npz files that are
 committed, so the parity tests can run where the reference is not available.
 
-Usage:  python tests/golden/make_golden.py [--reference /root/reference]
+Usage:  python tests/golden/make_golden.py [--reference /path/to/reference]
 """
 import argparse
 import os
@@ -141,7 +141,7 @@ def api_level(reference):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=build_ref.DEFAULT_REFERENCE)
     a = ap.parse_args()
     if build_ref.build(a.reference) is None:
         raise SystemExit("reference sources not found; cannot generate golden vectors")
