@@ -1,52 +1,69 @@
+"""Nested wall-clock sections.
+
+    with Profiler('outer'):
+        with Profiler('inner'):
+            ...
+
+prints, when the outermost section closes, one line per section indented by nesting depth
+(same usage and output shape as the reference's ``numml/profiler.py:4-55``).  Unlike the reference,
+the device is synchronised when a section opens and closes (``Profiler.sync``), so asynchronous
+CUDA work is charged to the section that enqueued it.
+"""
 import time
 
 
-class Profiler:
-    """Nested wall-clock sections: ``with Profiler('label'): ...`` prints a tree of timings when
-    the outermost section closes (reference ``numml/profiler.py:4-55``).  With ``sync=True`` the
-    CUDA device is synchronised at both ends so that asynchronous kernels are charged to the
-    section that launched them."""
+class _Node:
+    __slots__ = ("label", "parent", "children", "t0", "seconds")
 
-    enabled = True
-    current = None
+    def __init__(self, label, parent):
+        self.label, self.parent, self.children = label, parent, []
+        self.t0 = self.seconds = 0.0
+        if parent is not None:
+            parent.children.append(self)
+
+    def lines(self, depth, width):
+        yield f"{' ' * (depth * width)}[{self.label}] {self.seconds:.5f}s"
+        for child in self.children:
+            yield from child.lines(depth + 1, width)
+
+
+def _device_barrier():
+    import torch
+    if torch.cuda.is_available() and torch.cuda.is_initialized():
+        torch.cuda.synchronize()
+
+
+class Profiler:
+    enabled = True      # set False to turn every section into a no-op
+    sync = True         # synchronise the CUDA device at section boundaries
     tab_width = 2
-    sync = True
+    current = None      # innermost open section (a _Node), or None
 
     def __init__(self, section_name):
         self.section_name = section_name
-        self.children = []
-        self.parent = None
-        self.running_time = 0.0
-
-    @staticmethod
-    def _sync():
-        if Profiler.sync:
-            import torch
-            if torch.cuda.is_available():
-                torch.cuda.synchronize()
+        self._node = None
 
     def __enter__(self):
-        if not Profiler.enabled:
-            return self
-        self.parent = Profiler.current
-        if self.parent is not None:
-            self.parent.children.append(self)
-        Profiler.current = self
-        Profiler._sync()
-        self.start_time = time.perf_counter()
+        if Profiler.enabled:
+            self._node = _Node(self.section_name, Profiler.current)
+            Profiler.current = self._node
+            if Profiler.sync:
+                _device_barrier()
+            self._node.t0 = time.perf_counter()
         return self
 
-    def report(self, level=0):
-        print(' ' * (level * Profiler.tab_width) + f'[{self.section_name}] {self.running_time:.5f}s')
-        for child in self.children:
-            child.report(level + 1)
-
     def __exit__(self, exc_type, exc, tb):
-        if not Profiler.enabled:
+        node = self._node
+        if node is None:
             return False
-        Profiler._sync()
-        self.running_time = time.perf_counter() - self.start_time
-        Profiler.current = self.parent
-        if self.parent is None and exc_type is None:
-            self.report()
+        if Profiler.sync:
+            _device_barrier()
+        node.seconds = time.perf_counter() - node.t0
+        Profiler.current = node.parent
+        if node.parent is None and exc_type is None:
+            print("\n".join(node.lines(0, Profiler.tab_width)))
         return False
+
+    @property
+    def running_time(self):
+        return self._node.seconds if self._node is not None else 0.0

@@ -96,14 +96,15 @@ def test_stencils_bit_exact(oracle, ops, n, dtype):
     assert_same(gx_ref, gx, "grad_x")
 
 
-def test_int64_index_path(oracle, ops):
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+def test_int64_index_path(oracle, ops, dtype):
     """The kernels also read the int64 arrays exactly as the reference stores them."""
     from numml_b200 import _plan
     _plan.force_int64 = True
     _plan.clear_plan_cache()
     try:
-        d, i, p, (m, n) = W.poisson3d_7pt(24, torch.float64)
-        x, g = W.randn(n, 0, torch.float64), W.randn(m, 1, torch.float64)
+        d, i, p, (m, n) = W.poisson3d_7pt(24, dtype)
+        x, g = W.randn(n, 0, dtype), W.randn(m, 1, dtype)
         dd, di, dp, dx, dg = dev(d, i, p, x, g)
         assert_same(oracle.spgemv_forward(m, n, d, i, p, x), ops.spgemv_forward(m, n, dd, di, dp, dx), "y")
         gA_ref, gx_ref = oracle.spgemv_backward(g, m, n, d, i, p, x)
