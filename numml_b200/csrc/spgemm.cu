@@ -9,9 +9,10 @@
 //     bin 3: 256 threads per row, table in a caller-provided global-memory spill area
 // Column keys are inserted with atomicCAS and linear probing (load factor <= 1/2); the numeric
 // phase accumulates values with shared/global atomics and then emits the row in ascending column
-// order: 64-slot tables by counting, for every occupied slot, the smaller keys in the table (its
-// position in the sorted row), larger tables by a bitonic sort of the whole table (empty slots
-// sort last) followed by a copy of the first nnz entries.  The pattern is
+// order: for 64-slot tables the occupied slots are gathered into a dense list and every entry is
+// placed at the number of smaller keys in that list (its position in the sorted row); larger
+// tables are bitonic-sorted as a whole (empty slots sort last) and their first nnz entries
+// copied out.  The pattern is
 // purely structural: a product that cancels numerically still yields a stored zero, as in the
 // reference.
 //
@@ -226,6 +227,10 @@ spgemm_numeric_kernel(const int32_t* __restrict__ list, const unsigned long long
     constexpr int TABLE = SPILL ? 1 : (1 << TLOG);
     __shared__ uint32_t s_keys[TEAMS * TABLE];
     __shared__ T s_vals[TEAMS * TABLE];
+    constexpr int kListTeams = (!SPILL && TABLE <= 64) ? TEAMS : 1;   // dense lists only exist for tiny tables
+    __shared__ uint32_t s_list[kListTeams * 32];
+    __shared__ unsigned char s_slot[kListTeams * 32];
+    __shared__ int s_cnt[kListTeams];
     const int team = threadIdx.x / TEAM, t = threadIdx.x % TEAM;
     const int64_t count = (int64_t)*count_ptr;
     for (int64_t base = (int64_t)blockIdx.x * TEAMS; base < count; base += (int64_t)gridDim.x * TEAMS) {
@@ -263,19 +268,30 @@ spgemm_numeric_kernel(const int32_t* __restrict__ list, const unsigned long long
         }
         team_sync<TEAM>();
         if (!SPILL && TABLE <= 64) {
-            // tiny tables: the position of a column in the sorted row is the number of smaller
-            // columns in the table (empty slots hold the largest key); no sort, no data movement
+            // tiny tables: gather the occupied slots into a dense list (any order), then the position
+            // of a column in the sorted row is the number of smaller columns in that list; no sort,
+            // and the quadratic part runs over the row's nnz (<= 32) instead of the table size
+            if (t == 0) s_cnt[team] = 0;
+            team_sync<TEAM>();
+            for (int sl = t; sl < TABLE; sl += TEAM) {
+                const uint32_t key = keys[sl];
+                if (key != kEmptyKey) {
+                    const int pos = atomicAdd(&s_cnt[team], 1);
+                    s_list[team * 32 + pos] = key;
+                    s_slot[team * 32 + pos] = (unsigned char)sl;
+                }
+            }
+            team_sync<TEAM>();
             if (active) {
                 const int64_t o0 = C_indptr[row];
-                for (int sl = t; sl < TABLE; sl += TEAM) {
-                    const uint32_t key = keys[sl];
-                    if (key != kEmptyKey) {
-                        int rank = 0;
-#pragma unroll 8
-                        for (int q = 0; q < TABLE; ++q) rank += keys[q] < key;
-                        C_indices[o0 + rank] = (int64_t)key;
-                        C_data[o0 + rank] = vals[sl];
-                    }
+                const int n = s_cnt[team];
+                const uint32_t* lst = s_list + team * 32;
+                for (int e = t; e < n; e += TEAM) {
+                    const uint32_t key = lst[e];
+                    int rank = 0;
+                    for (int q = 0; q < n; ++q) rank += lst[q] < key;
+                    C_indices[o0 + rank] = (int64_t)key;
+                    C_data[o0 + rank] = vals[s_slot[team * 32 + e]];
                 }
             }
         } else {
