@@ -263,6 +263,12 @@ NB200_API int nb200_spgemm_backward(int64_t A_rows, int64_t A_cols, int64_t A_nn
  *                        progress the kernel stores NB200_ERR_WAIT_BUDGET in the device word `status`
  *                        (which the caller zeroes beforehand and reads afterwards), writes NaN into the
  *                        affected rows and returns; it never spins without a limit.
+ *                        `team_lanes` (0, or a power of two up to 32) is the least number of lanes
+ *                        given to one row; 0 means the smallest power of two that covers `nrhs`.
+ *                        A warp's poll takes as long as its slowest row, so when the levels are
+ *                        narrow (n / levels well below the number of resident warps) a full warp per
+ *                        row is fastest even though the spare lanes idle; with wide levels fewer
+ *                        lanes per row keep the GPU full.  The result does not depend on it.
  * nb200_masked_outer     out[k] = sum_r alpha * (a[row(k), r] * b[col(k), r]): the masked outer
  *                        product grad_A = -(grad_b x^T) on the pattern of A (alpha = -1), summed over
  *                        the right-hand sides in ascending order.
@@ -276,7 +282,7 @@ NB200_API int nb200_sptrsv_solve(int64_t n, int64_t nnz, int64_t nrhs,
                                  const void* data, const void* indices, const void* indptr, const void* perm,
                                  const int32_t* order, int lower, int unit, const void* b, void* x,
                                  double* x_double, int32_t* status, int64_t wait_budget_cycles,
-                                 int dtype, int itype, nb200_stream stream);
+                                 int team_lanes, int dtype, int itype, nb200_stream stream);
 NB200_API int nb200_masked_outer(int64_t rows, int64_t nnz, int64_t nrhs, const void* indices, const void* indptr,
                                  const void* a, const void* b, double alpha, void* out,
                                  int dtype, int itype, nb200_stream stream);

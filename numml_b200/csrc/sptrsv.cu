@@ -116,6 +116,7 @@ sptrsv_syncfree_kernel(int64_t n, int64_t nrhs, const T* __restrict__ data, cons
 
     for (int64_t c = tl; c < nrhs; c += TS) {              // this lane's right-hand sides
         double acc = 0.0, diag = 0.0;
+        const double bi = (double)b[i * nrhs + c];         // fetched before the waits, off the critical path
         bool stop = false;
         // lower: ascending from the row start; upper: descending from the row end
         for (int64_t q = 0; q < len && !stop && ok; q += D) {
@@ -140,11 +141,20 @@ sptrsv_syncfree_kernel(int64_t n, int64_t nrhs, const T* __restrict__ data, cons
             }
             long long t0 = 0;
             for (unsigned spins = 0; pend != 0; ++spins) {
+                // Issue every outstanding poll before looking at any answer: the loads are then in
+                // flight together and one round costs one L2 round trip, not one per dependency.
+                const unsigned asked = pend;
+                long long bits[D];
 #pragma unroll
                 for (int d = 0; d < D; ++d) {
-                    if ((pend >> d) & 1u) {
-                        const long long bits = ld_relaxed_bits(xd + jj[d] * nrhs + c);
-                        if (bits != kNotReady) { xv[d] = __longlong_as_double(bits); pend &= ~(1u << d); }
+                    bits[d] = kNotReady;
+                    if ((asked >> d) & 1u) bits[d] = ld_relaxed_bits(xd + jj[d] * nrhs + c);
+                }
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    if (((asked >> d) & 1u) && bits[d] != kNotReady) {
+                        xv[d] = __longlong_as_double(bits[d]);
+                        pend &= ~(1u << d);
                     }
                 }
                 if (pend != 0) {
@@ -165,7 +175,7 @@ sptrsv_syncfree_kernel(int64_t n, int64_t nrhs, const T* __restrict__ data, cons
         }
         double xi;
         if (ok) {
-            xi = (double)b[i * nrhs + c] - acc;
+            xi = bi - acc;
             if (!unit) xi /= diag;
             if (__double_as_longlong(xi) == kNotReady) xi = canonical_nan;   // never publish the marker itself
         } else {
@@ -309,8 +319,9 @@ extern "C" int nb200_sptrsv_solve(int64_t n, int64_t nnz, int64_t nrhs,
                                   const void* data, const void* indices, const void* indptr, const void* perm,
                                   const int32_t* order, int lower, int unit, const void* b, void* x,
                                   double* x_double, int32_t* status, int64_t wait_budget_cycles,
-                                  int dtype, int itype, nb200_stream stream) {
+                                  int team_lanes, int dtype, int itype, nb200_stream stream) {
     if (n < 0 || nnz < 0 || nrhs < 0) return NB200_ERR_BAD_ARG;
+    if (team_lanes < 0 || team_lanes > 32 || (team_lanes & (team_lanes - 1)) != 0) return NB200_ERR_BAD_ARG;
     if (n == 0 || nrhs == 0) return NB200_OK;
     if (!indptr || !order || !b || !x || !status || (nnz > 0 && (!data || !indices))) return NB200_ERR_BAD_ARG;
     if (dtype == NB200_F32 && !x_double) return NB200_ERR_BAD_ARG;
@@ -319,6 +330,7 @@ extern "C" int nb200_sptrsv_solve(int64_t n, int64_t nnz, int64_t nrhs,
     if (cudaMemsetAsync(xd_all, 0xff, sizeof(double) * (size_t)n * (size_t)nrhs, st) != cudaSuccess) return NB200_ERR_CUDA;
     int ts = 1;
     while (ts < 32 && ts < nrhs) ts <<= 1;
+    if (team_lanes > ts) ts = team_lanes;   // spare lanes idle; fewer rows share a warp's poll round trips
     const long long budget = wait_budget_cycles > 0 ? wait_budget_cycles : 2000000000LL;
     return NB200_DISPATCH(dtype, itype, ([&]() -> int {
         double* xd = (dtype == NB200_F64) ? (double*)x : x_double;
@@ -390,5 +402,5 @@ extern "C" int nb200_sptrsv_solve_f32_noalloc(int64_t n, int64_t nnz, int64_t nr
     // nb200_sptrsv_solve refills the working array with the "not solved yet" marker on every call,
     // so whatever the previous call left in the shared region is never read.
     return nb200_sptrsv_solve(n, nnz, nrhs, data, indices, indptr, perm, order, lower, unit, b, x, words, status,
-                              wait_budget_cycles, NB200_F32, itype, stream);
+                              wait_budget_cycles, /*team_lanes=*/0, NB200_F32, itype, stream);
 }

@@ -299,6 +299,7 @@ def spgemm_backward(grad_C, C_indices, C_indptr, A_rows, A_cols, A_data, A_indic
 # Poll budget of the solve kernel in SM cycles (about a second) and whether every solve reads the
 # device status word back (one small synchronising copy) so that an expired wait raises at once.
 sptrsv_wait_budget_cycles = 2_000_000_000
+_RESIDENT_THREADS = 148 * 2048               # threads a B200 keeps resident at once
 sptrsv_check_status = True
 
 
@@ -314,7 +315,18 @@ def check_status(device=None):
                            f"{_cabi.lib().nb200_status_string(code).decode()} (results of the affected call hold NaN)")
 
 
-def _solve(plan, data, idx, ptr, perm, itype, order, lower, unit, b):
+def _team_lanes(n, nlevels):
+    """Lanes per row for the triangular solve.  With narrow levels the solve is bound by the chain of
+    poll round trips, and a warp that holds one row is not held up by the slowest of several; with
+    wide levels the rows of a level fill the GPU and the lanes are better spent on more rows."""
+    width = n / max(int(nlevels), 1)                     # average rows per level
+    lanes = 32
+    while lanes > 1 and width * lanes > _RESIDENT_THREADS:
+        lanes //= 2
+    return lanes
+
+
+def _solve(plan, data, idx, ptr, perm, itype, order, nlevels, lower, unit, b):
     n = plan.rows
     nrhs = 1 if b.ndim == 1 else int(b.shape[1])
     dev = b.device
@@ -324,7 +336,7 @@ def _solve(plan, data, idx, ptr, perm, itype, order, lower, unit, b):
     _cabi.call("nb200_sptrsv_solve", n, plan.nnz, nrhs, _ptr(data), _ptr(idx), _ptr(ptr),
                _ptr(perm) if perm is not None else None, _ptr(order), int(bool(lower)), int(bool(unit)),
                _ptr(b), _ptr(x), _ptr(xd) if xd is not None else None, _ptr(status),
-               int(sptrsv_wait_budget_cycles), _dtype_code(data), itype, _stream())
+               int(sptrsv_wait_budget_cycles), _team_lanes(n, nlevels), _dtype_code(data), itype, _stream())
     if sptrsv_check_status:
         check_status(dev)
     return x
@@ -345,8 +357,8 @@ def sptrsv_forward(A_rows, A_cols, A_data, A_indices, A_indptr, lower, unit, b):
     plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
     idx, ptr, itype = plan.csr()
     with _on(dev):
-        order, _ = plan.sptrsv_order(lower)
-        return _solve(plan, A_data, idx, ptr, None, itype, order, lower, unit, b)
+        order, nlevels = plan.sptrsv_order(lower)
+        return _solve(plan, A_data, idx, ptr, None, itype, order, nlevels, lower, unit, b)
 
 
 def sptrsv_backward(grad_x, x, A_rows, A_cols, A_data, A_indices, A_indptr, lower, unit, b):
@@ -359,9 +371,9 @@ def sptrsv_backward(grad_x, x, A_rows, A_cols, A_data, A_indices, A_indptr, lowe
     nrhs = 1 if x.ndim == 1 else int(x.shape[1])
     with _on(dev):
         t_indptr, t_indices, t_perm, _ = plan.transpose()
-        order_t, _ = plan.sptrsv_order(not lower, transposed=True)
+        order_t, nlevels_t = plan.sptrsv_order(not lower, transposed=True)
         # grad_b = A^{-T} grad_x: the opposite-triangle solve on the transposed structure
-        grad_b = _solve(plan, A_data, t_indices, t_indptr, t_perm, itype, order_t, not lower, unit, grad_x)
+        grad_b = _solve(plan, A_data, t_indices, t_indptr, t_perm, itype, order_t, nlevels_t, not lower, unit, grad_x)
         grad_A = torch.empty_like(A_data)
         _cabi.call("nb200_masked_outer", A_rows, plan.nnz, nrhs, _ptr(idx), _ptr(ptr), _ptr(grad_b), _ptr(x), -1.0,
                    _ptr(grad_A), _dtype_code(A_data), itype, _stream())

@@ -133,7 +133,7 @@ def test_wait_budget_expires_cleanly(ops):
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
     _cabi.call("nb200_sptrsv_solve", n, d.numel(), 1, P(dd), P(i32), P(p32), None, P(order), 1, 0, P(b), P(x),
-               None, P(status), 2_000_000, _cabi.F64, _cabi.I32,
+               None, P(status), 2_000_000, 0, _cabi.F64, _cabi.I32,
                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     assert int(status.item()) == 5          # NB200_ERR_WAIT_BUDGET

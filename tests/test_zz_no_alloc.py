@@ -44,7 +44,7 @@ def test_noalloc_solve_matches_regular_entry_point(n, nrhs, lower):
         x_ref = torch.empty_like(b)
         xd = torch.empty(n * nrhs, dtype=torch.float64, device="cuda")
         _cabi.call("nb200_sptrsv_solve", n, nnz, nrhs, P(data), P(idx), P(ptr), None, P(order), int(lower), 0,
-                   P(b), P(x_ref), P(xd), P(status), 0, _cabi.F32, itype, stream)
+                   P(b), P(x_ref), P(xd), P(status), 0, 0, _cabi.F32, itype, stream)
         x = torch.full_like(b, float("nan"))
         _cabi.call("nb200_sptrsv_solve_f32_noalloc", n, nnz, nrhs, P(data), P(idx), P(ptr), None, P(order),
                    int(lower), 0, P(b), P(x), P(status), 0, itype, stream)
