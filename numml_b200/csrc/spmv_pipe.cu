@@ -18,6 +18,9 @@
 //   kGradA         stage = column indices                      grad_A[k] = g[row(k)] x[col[k]]
 //   kBackwardSym   stage = column indices + permutation        both gradients in one pass, for patterns that
 //                                                              equal their transpose (stencils, undirected graphs)
+// The fused backward gathers three operands per entry (x, g and the transposed value).  Its row threads
+// fetch them with per-thread asynchronous copies (cp.async) into shared-memory slots instead of into
+// registers, eight entries at a time, so that a short row has all of its gathers in flight at once.
 //
 // Every wait on an mbarrier is a bounded try_wait loop; if the bound is hit the CTA records
 // NB200_ERR_WAIT_BUDGET in the status word (when one is given) and leaves its block loop.
@@ -78,7 +81,11 @@ struct PipeArgs {
     int32_t* status;     // may be null
 };
 
-template <typename T, typename I, int MODE, int S, bool DIRECT = false>
+// GATHER > 0 (kBackwardSym with direct grad_A stores only): a row thread fetches x_c, g_c and the
+// transposed value of GATHER entries at a time with asynchronous copies into shared-memory slots of
+// its own instead of into registers.  All gathers of a short row are then in flight at once and a
+// block costs one memory round trip, where the register version needs one per CH entries.
+template <typename T, typename I, int MODE, int S, bool DIRECT = false, int GATHER = 0>
 struct PipeSmem {
     static constexpr bool has_a = MODE != kGradA;
     static constexpr bool a_is_perm = MODE == kForwardPerm || MODE == kBackwardSym;
@@ -88,8 +95,21 @@ struct PipeSmem {
     static constexpr size_t p_bytes = has_p ? sizeof(T) * kPipeTile : 0;                               // grad_A staging
     static constexpr size_t stage_bytes = a_bytes + b_bytes + p_bytes;
     static constexpr size_t header_bytes = 128;
-    static constexpr size_t total = header_bytes + stage_bytes * S;
+    // three planes (g_c, transposed value, x_c) of one slot per (entry position, consumer thread)
+    static constexpr size_t gather_bytes = 3 * sizeof(T) * GATHER * kPipeConsumers;
+    static constexpr size_t total = header_bytes + stage_bytes * S + gather_bytes;
+    static_assert(GATHER == 0 || (MODE == kBackwardSym && DIRECT), "GATHER is a variant of the fused backward");
 };
+
+template <typename T> struct Pair;
+template <> struct Pair<float> { using type = float2; };
+template <> struct Pair<double> { using type = double2; };
+
+// 4- or 8-byte asynchronous copy global -> shared into a slot owned by the issuing thread
+template <typename T>
+__device__ __forceinline__ void async_copy_elem(T* dst, const T* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" :: "r"(smem_u32(dst)), "l"(src), "n"(sizeof(T)) : "memory");
+}
 
 template <typename T>
 __device__ __forceinline__ void lds4(const T* p, T (&v)[4]);
@@ -125,10 +145,10 @@ __device__ __forceinline__ void sts4<double>(double* p, const double (&v)[4]) {
     *reinterpret_cast<double2*>(p + 2) = make_double2(v[2], v[3]);
 }
 
-template <typename T, typename I, int MODE, int S, int CH, int MINB, bool DIRECT>
+template <typename T, typename I, int MODE, int S, int CH, int MINB, bool DIRECT, int GATHER>
 __global__ void __launch_bounds__(kPipeThreads, MINB)
 spmv_pipe_kernel(const PipeArgs<T, I> a) {
-    using L = PipeSmem<T, I, MODE, S, DIRECT>;
+    using L = PipeSmem<T, I, MODE, S, DIRECT, GATHER>;
     constexpr int kPipeStages = S;
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -237,7 +257,50 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
         T* const outp = a.out + base;                                // entry with stage offset o is out[base + o]
 
         // ---- one thread per row: entries from the stage, x through L1/L2, storage order ----
-        if (owns_row) {
+        if (MODE == kBackwardSym && GATHER > 0) {
+            if (owns_row) {
+                using T2 = typename Pair<T>::type;
+                constexpr int kPlane = GATHER * kPipeConsumers;
+                T* const sg = reinterpret_cast<T*>(smem + L::header_bytes + (size_t)kPipeStages * L::stage_bytes) + tid;
+                T* const sd = sg + kPlane;
+                T* const sx = sd + kPlane;
+                const int o_lo = cur.lo + shift, o_hi = cur.hi + shift;
+                const int o_staged = min(o_hi, staged_cnt);              // below o_hi only at the ragged end of the arrays
+                const T gi = cur.g;
+                T acc = 0;
+                for (int o0 = o_lo; o0 < o_staged; o0 += GATHER) {
+                    const int n = min(GATHER, o_staged - o0);
+                    // (1) every gather of the chunk at once: x_c, g_c and A^T[i, c] = data[perm[k]]
+                    for (int e = 0; e < n; ++e) {
+                        const I c = sidx[o0 + e], q = sperm[o0 + e];
+                        async_copy_elem(sx + e * kPipeConsumers, a.vec + c);
+                        async_copy_elem(sg + e * kPipeConsumers, a.rowvec + c);
+                        async_copy_elem(sd + e * kPipeConsumers, a.data + q);
+                    }
+                    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+                    // (2) grad_A[k] = g_i x_c, two entries per vector store where the address allows
+                    int e = 0;
+                    if (o0 & 1) { outp[o0] = mul_rn(gi, sx[0]); e = 1; }
+                    for (; e + 2 <= n; e += 2) {
+                        T2 w;
+                        w.x = mul_rn(gi, sx[e * kPipeConsumers]);
+                        w.y = mul_rn(gi, sx[(e + 1) * kPipeConsumers]);
+                        *reinterpret_cast<T2*>(outp + o0 + e) = w;
+                    }
+                    if (e < n) outp[o0 + e] = mul_rn(gi, sx[e * kPipeConsumers]);
+                    // (3) grad_x[i] += A^T[i, c] g_c in storage order
+#pragma unroll
+                    for (int j = 0; j < GATHER; ++j)
+                        if (j < n) acc = add_rn(acc, mul_rn(sg[j * kPipeConsumers], sd[j * kPipeConsumers]));
+                }
+                for (int o = max(o_staged, o_lo); o < o_hi; ++o) {       // entries that were not staged: plain loads
+                    const I c = a.indices[base + o];
+                    outp[o] = mul_rn(gi, ldg(a.vec + c));
+                    acc = add_rn(acc, mul_rn(ldg(a.rowvec + c), ldg(a.data + a.perm[base + o])));
+                }
+                a.out2[r0 + tid] = acc;
+            }
+        } else if (owns_row) {
             T acc = 0;
             const int o_lo = cur.lo + shift, o_hi = cur.hi + shift;
             const bool all_staged = o_hi <= staged_cnt;              // false only at the ragged end of the arrays
@@ -325,11 +388,11 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
     }
 }
 
-template <typename T, typename I, int MODE, int S, int CH = 8, int MINB = 3, bool DIRECT = false>
+template <typename T, typename I, int MODE, int S, int CH = 8, int MINB = 3, bool DIRECT = false, int GATHER = 0>
 int spmv_pipe_launch(const PipeArgs<T, I>& args, cudaStream_t st) {
-    using L = PipeSmem<T, I, MODE, S, DIRECT>;
+    using L = PipeSmem<T, I, MODE, S, DIRECT, GATHER>;
     static bool configured = false;
-    auto kernel = spmv_pipe_kernel<T, I, MODE, S, CH, MINB, DIRECT>;
+    auto kernel = spmv_pipe_kernel<T, I, MODE, S, CH, MINB, DIRECT, GATHER>;
     if (!configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::total) != cudaSuccess)
             return NB200_ERR_CUDA;
@@ -367,13 +430,14 @@ int spmv_pipe_backward_sym(int64_t row_begin, int64_t row_end, int64_t nnz, int 
                            T* grad_x, int32_t* status, cudaStream_t st) {
     if (row_end <= row_begin) return NB200_OK;
     PipeArgs<T, I> a{row_begin, row_end, nnz, ceil_div(row_end - row_begin, (int64_t)block_rows), block_rows, data, indices, indptr, perm, x, g, grad_A, grad_x, status};
-    // four stages, four entries per gather round, grad_A written straight from the row threads:
-    // the best of the measured variants (staged + coalesced grad_A stores cost a third of the
-    // shared memory and with it the pipeline depth)
-    // Measured on the 128^3 Poisson matrix (us): 2 stages / 2 entries per gather round / 4 CTAs per SM 94.5;
-    // 2/4/4 98; 4/4/3 104; 3/8/3 112; anything that needs 5+ CTAs per SM spills and is slower; staging
-    // grad_A in shared memory for coalesced stores costs more occupancy than it saves (107).
-    return spmv_pipe_launch<T, I, kBackwardSym, 2, 2, 4, true>(a, st);
+    // Measured on the 128^3 Poisson matrix (us).  Gathers into registers, grad_A written straight from the
+    // row threads: 2 stages / 2 entries per round / 4 CTAs per SM 94.5; 2/4/4 98; 4/4/3 104; 3/8/3 112; 5+ CTAs
+    // per SM spill; grad_A staged in shared memory for coalesced stores 107.  Asynchronous gathers into
+    // per-thread slots, 8 entries at a time, 2 stages, 2 CTAs per SM: 85.8.  On top of that: 3 CTAs per SM
+    // (7 or 6 slots) 133 -- the L1 that the gathers land in shrinks to a few KB; x through registers 88-98; a
+    // single stage 97-128; staging the block's own slice of `data` 95; staging grad_A over the dead index
+    // area 101; fetching the transposed value as an L1-bypassing 16-byte group 103.
+    return spmv_pipe_launch<T, I, kBackwardSym, 2, 2, 2, true, 8>(a, st);
 }
 
 #define NB200_INSTANTIATE_PIPE(T, I)                                                                                 \

@@ -96,6 +96,52 @@ def test_stencils_bit_exact(oracle, ops, n, dtype):
     assert_same(gx_ref, gx, "grad_x")
 
 
+def _symmetric_pattern_case(kind, dtype):
+    """A matrix whose PATTERN equals its transpose while its VALUES do not (they are random), so that
+    a backward pass that confused an entry with its mirror image would be caught."""
+    import numpy as np
+    import scipy.sparse as sps
+    if kind == "stencil7":                      # every row has at most 7 entries
+        _, i, p, (n, _) = W.poisson3d_7pt(20, dtype)
+        S = sps.csr_matrix((np.ones(i.numel()), i.numpy(), p.numpy()), shape=(n, n))
+    elif kind == "stencil9":                    # interior rows have 9 entries
+        _, i, p, (n, _) = W.poisson2d_9pt_lower(70, dtype)
+        L = sps.csr_matrix((np.ones(i.numel()), i.numpy(), p.numpy()), shape=(n, n))
+        S = (L + L.T).tocsr()
+    else:                                       # short random rows plus a few rows of 60+ entries
+        n = 6000
+        rng = np.random.default_rng(5)
+        B = sps.random(n, n, density=2.0 / n, random_state=7, format="lil")
+        for h in rng.choice(n, 12, replace=False):
+            B[h, rng.choice(n, 60, replace=False)] = 1.0
+        B = B.tocsr()
+        S = (B + B.T + sps.eye(n)).tocsr()
+    S.sort_indices()
+    indices = torch.from_numpy(S.indices.astype(np.int64))
+    indptr = torch.from_numpy(S.indptr.astype(np.int64))
+    data = W.randn(indices.numel(), 3, dtype)
+    return data, indices, indptr, S.shape
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+@pytest.mark.parametrize("kind", ["stencil7", "stencil9", "hubs"])
+def test_symmetric_pattern_random_values_bit_exact(oracle, ops, kind, dtype):
+    """The one-pass backward for patterns that equal their transpose, on values that are not
+    symmetric: rows short enough for the asynchronous gathers, rows just beyond them, and blocks
+    that mix short rows with long ones."""
+    from numml_b200 import _plan
+    d, i, p, (m, k) = _symmetric_pattern_case(kind, dtype)
+    x, g = W.randn(k, 0, dtype), W.randn(m, 1, dtype)
+    dd, di, dp, dx, dg = dev(d, i, p, x, g)
+    plan = _plan.get_plan(m, k, di, dp)
+    assert plan.pattern_symmetric() and plan.spmv_block_rows() > 0
+    assert_same(oracle.spgemv_forward(m, k, d, i, p, x), ops.spgemv_forward(m, k, dd, di, dp, dx), "y")
+    gA_ref, gx_ref = oracle.spgemv_backward(g, m, k, d, i, p, x)
+    gA, gx = ops.spgemv_backward(dg, m, k, dd, di, dp, dx)
+    assert_same(gA_ref, gA, "grad_A")
+    assert_same(gx_ref, gx, "grad_x")
+
+
 @pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
 def test_int64_index_path(oracle, ops, dtype):
     """The kernels also read the int64 arrays exactly as the reference stores them."""
