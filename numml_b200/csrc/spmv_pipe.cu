@@ -25,6 +25,7 @@
 // Every wait on an mbarrier is a bounded try_wait loop; if the bound is hit the CTA records
 // NB200_ERR_WAIT_BUDGET in the status word (when one is given) and leaves its block loop.
 #include "spmv_pipe.cuh"
+#include <atomic>
 
 namespace nb200 {
 
@@ -32,6 +33,7 @@ constexpr int kPipeTile = kSpmvPipeTile;   // nonzeros per stage
 constexpr int kPipeConsumers = 256;   // consumer threads (8 warps); one more warp produces
 constexpr int kPipeThreads = kPipeConsumers + 32;
 constexpr unsigned kPipeSpinLimit = 1u << 24;
+constexpr int kMaxDevices = 64;        // devices one process can address
 
 enum PipeMode { kForward = 0, kForwardPerm = 1, kGradA = 2, kBackwardSym = 3 };
 
@@ -391,12 +393,15 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
 template <typename T, typename I, int MODE, int S, int CH = 8, int MINB = 3, bool DIRECT = false, int GATHER = 0>
 int spmv_pipe_launch(const PipeArgs<T, I>& args, cudaStream_t st) {
     using L = PipeSmem<T, I, MODE, S, DIRECT, GATHER>;
-    static bool configured = false;
+    // the opt-in to more than 48 KB of dynamic shared memory is a per-device property of the kernel
+    static std::atomic<bool> configured[kMaxDevices];
     auto kernel = spmv_pipe_kernel<T, I, MODE, S, CH, MINB, DIRECT, GATHER>;
-    if (!configured) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return NB200_ERR_CUDA;
+    if (!configured[device].load(std::memory_order_acquire)) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::total) != cudaSuccess)
             return NB200_ERR_CUDA;
-        configured = true;
+        configured[device].store(true, std::memory_order_release);
     }
     int per_sm = (int)((size_t)(227 * 1024) / (L::total + 1024));
     if (per_sm > MINB) per_sm = MINB;

@@ -106,3 +106,15 @@ def test_linear_operator_and_profiler(capsys):
             pass
     out = capsys.readouterr().out
     assert "[outer]" in out and "  [inner]" in out
+
+
+def test_triangular_solve_team_size_follows_level_width():
+    """Lanes per row for the triangular solve: a whole warp when the dependency levels are narrow
+    (latency-bound), fewer lanes as the average level gets wide enough to fill the GPU by itself."""
+    from numml_b200 import numml_torch_cpp as ops
+    assert ops._team_lanes(1 << 20, 3070) == 32            # 9-point factor on a 1024^2 grid: 341 rows per level
+    assert ops._team_lanes(1000, 1000) == 32               # a chain
+    assert ops._team_lanes(1 << 20, 1) == 1                # diagonal matrix: one level holds every row
+    wide = ops._team_lanes(1 << 22, 100)                   # 42 k rows per level
+    assert wide in (1, 2, 4, 8) and 42000 * wide <= 148 * 2048 < 42000 * wide * 2
+    assert ops._team_lanes(5, 0) == 32                     # no levels recorded (empty matrix): harmless
