@@ -1,7 +1,7 @@
 """Per-operator measurements for the five benchmark configurations, with the reference CPU path
 timed beside each one.
 
-    python -m numml_b200.benchmarks [--configs 1,2,3,4,5] [--no-cpu]
+    python -m numml_b200.benchmarks [--configs 1,2,3,4,5] [--no-cpu]        (6 = one GCN layer on the C3 graph)
 
 Prints a Markdown table: CUDA-event time of each operator through the operator functions (plan
 cached, median of the repetitions), its algorithmic bytes and effective bandwidth as a fraction of
@@ -228,6 +228,40 @@ def config5(rep, ops, W, cpu, n=1024):
             "one right-hand side x 16 (the reference transposes per call)", "")
 
 
+def config6(rep, W, n=1 << 22):
+    """One graph-convolution layer (the caller of the C3 SpMM): GCNConv(128 -> 128) with degree
+    normalisation on the power-law graph, forward alone and a full training step (forward + backward
+    with gradients for the layer parameters, the stored values of A and the node features)."""
+    import numml_b200.nn as gnn
+    import numml_b200.sparse as sp
+    d, i, p, (m, k) = W.powerlaw_graph(n, scale=4, seed=0, dtype=torch.float32)
+    K = 128
+    name = f"C3 graph, GCNConv({K}->{K}, normalised), {n} nodes, {d.numel()} nnz, fp32"
+    A = sp.SparseCSRTensor((d.cuda(), i.cuda(), p.cuda()), (m, k), clone=False)
+    A.requires_grad = True
+    torch.manual_seed(0)
+    layer = gnn.GCNConv(K, K).cuda()
+    X = torch.randn((m, K), dtype=torch.float32, device="cuda", generator=torch.Generator("cuda").manual_seed(0))
+    G = torch.randn((m, K), dtype=torch.float32, device="cuda", generator=torch.Generator("cuda").manual_seed(1))
+    X.requires_grad_(True)
+
+    def forward_only():
+        with torch.no_grad():
+            return layer(A, X)
+
+    def step():
+        A.data.grad = None
+        X.grad = None
+        layer.zero_grad(set_to_none=True)
+        layer(A, X).backward(G)
+
+    t_f = gpu_ms(forward_only, 5, 2)
+    t_s = gpu_ms(step, 5, 2)
+    # one row-sum pass over A, one SpMM, one 128x128 GEMM over the features and 5 element-wise passes
+    rep.add(name, "layer forward", t_f, None, None, "", "row sums + X W + SpMM + scaling; no CPU column (the reference layer is Python over its operators)")
+    rep.add(name, "layer forward + backward", t_s, None, None, "", "gradients for weights, bias, A.data and X")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="1,2,3,4,5")
@@ -249,6 +283,8 @@ def main():
             config4(rep, ops, W, cpu, 512 if a.small else 2048)
         elif c == 5:
             config5(rep, ops, W, cpu, 256 if a.small else 1024)
+        elif c == 6:
+            config6(rep, W, (1 << 18) if a.small else (1 << 22))
         torch.cuda.empty_cache()
     print(f"GPU: {torch.cuda.get_device_name(0)}; peak = {peak:.1f} GB/s ({kind} copy bandwidth); "
           f"CPU baseline: {cpu_kind}, 1 thread of {os.cpu_count()} host cores; index width read by the kernels: int32 plan copy\n")

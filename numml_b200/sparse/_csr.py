@@ -180,6 +180,30 @@ class spdmm(torch.autograd.Function):
         return None, grad_A, None, None, grad_B
 
 
+class sprowsum(torch.autograd.Function):
+    """Row sums of a CSR matrix (reference ``numml/sparse/_csr.py:416-439``).  On the device this is
+    the SpMV kernel applied to the all-ones vector: multiplying by one is exact and the kernel adds
+    in storage order, so the sums are those of the reference's sequential loop, bit for bit, and
+    do not depend on scheduling (an ``index_add`` would use atomics).  The gradient of a row sum
+    with respect to an entry is the upstream value of its row."""
+
+    @staticmethod
+    def forward(ctx, A_shape, A_data, A_indices, A_indptr):
+        ones = torch.ones(A_shape[1], dtype=A_data.dtype, device=A_data.device)
+        with Profiler('sprowsum forward'):
+            out = numml_torch_cpp.spgemv_forward(A_shape[0], A_shape[1], A_data, A_indices, A_indptr, ones)
+        ctx.save_for_backward(A_indptr)
+        ctx.nnz = A_data.numel()
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (A_indptr,) = ctx.saved_tensors
+        with Profiler('sprowsum backward'):
+            grad_A = grad_out.contiguous()[_row_ids(A_indptr, ctx.nnz)]
+        return None, grad_A, None, None
+
+
 # ---------------------------------------------------------------------------------------------
 # Pattern helpers written with torch tensor ops (differentiable through `data`)
 # ---------------------------------------------------------------------------------------------
@@ -390,6 +414,8 @@ class SparseCSRTensor(object):
         return self.data.sum()
 
     def row_sum(self):
+        if self.data.is_cuda:
+            return sprowsum.apply(self.shape, self.data, self.indices, self.indptr)
         out = torch.zeros(self.shape[0], dtype=self.data.dtype, device=self.device)
         return out.index_add(0, _row_ids(self.indptr, self.nnz), self.data)
 

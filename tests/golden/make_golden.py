@@ -136,6 +136,40 @@ def api_level(reference):
     out["galerkin/AH_indptr"] = npy(AH.indptr)
     out["galerkin/grad_A"] = npy(A.data.grad)
     out["galerkin/grad_P"] = npy(P.data.grad)
+
+    # graph-convolution layers (reference numml/nn.py:6-168): weights set explicitly, gradients with
+    # respect to the layer parameters, the stored values of A and the node features
+    import numml.nn as rnn
+    gd, gi, gp, gshape = W.random_csr(30, 30, 0.15, seed=61, dtype=torch.float32)
+    gd = gd.abs()                                  # row sums > -1 keep the normalisation real
+    out["gnn/A_data"], out["gnn/A_indices"], out["gnn/A_indptr"] = npy(gd), npy(gi), npy(gp)
+    X0 = W.randn((30, 4), 62, torch.float32)
+    out["gnn/X"] = npy(X0)
+
+    def run(tag, layer, w_seed):
+        with torch.no_grad():
+            layer.weights.copy_(W.randn(tuple(layer.weights.shape), w_seed, torch.float32))
+            layer.bias.copy_(W.randn(tuple(layer.bias.shape), w_seed + 1, torch.float32))
+        A = sp.SparseCSRTensor((gd.clone(), gi, gp), gshape)
+        A.requires_grad = True
+        X = X0.clone().requires_grad_(True)
+        Y = layer(A, X)
+        w = W.randn(tuple(Y.shape), w_seed + 2, torch.float32)
+        (Y * w).sum().backward()
+        out[f"gnn/{tag}/weights"] = npy(layer.weights)
+        out[f"gnn/{tag}/bias"] = npy(layer.bias)
+        out[f"gnn/{tag}/Y"] = npy(Y)
+        out[f"gnn/{tag}/w"] = npy(w)
+        out[f"gnn/{tag}/grad_weights"] = npy(layer.weights.grad)
+        out[f"gnn/{tag}/grad_bias"] = npy(layer.bias.grad)
+        out[f"gnn/{tag}/grad_A"] = npy(A.data.grad)
+        out[f"gnn/{tag}/grad_X"] = npy(X.grad)
+
+    run("gcn_norm", rnn.GCNConv(4, 3, normalize=True), 70)
+    run("gcn_plain", rnn.GCNConv(4, 3, normalize=False), 73)
+    run("tag_norm", rnn.TAGConv(4, 3, k=2, normalize=True), 76)
+    run("tag_plain", rnn.TAGConv(4, 3, k=3, normalize=False), 79)
+    out["rowsum/values"] = npy(sp.SparseCSRTensor((gd, gi, gp), gshape).row_sum())
     return out
 
 
