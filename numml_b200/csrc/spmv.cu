@@ -379,7 +379,8 @@ extern "C" int nb200_spgemv_backward_symmetric_rows(int64_t n, int64_t nnz, int6
     if (block_rows < 1 || block_rows > 256) return NB200_ERR_BAD_ARG;
     if (row_end == row_begin || nnz == 0) return NB200_OK;
     if (!data || !indices || !indptr || !t_perm || !x || !g || !grad_A || !grad_x) return NB200_ERR_BAD_ARG;
-    if (!aligned16(indices) || !aligned16(t_perm)) return NB200_ERR_ALIGN;
+    // bulk copies of the index streams and two-entry vector stores of grad_A
+    if (!aligned16(indices) || !aligned16(t_perm) || !aligned16(grad_A)) return NB200_ERR_ALIGN;
     if (itype == NB200_I32 && nnz > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
     return NB200_DISPATCH(dtype, itype,
         (spmv_pipe_backward_sym<T, I>(row_begin, row_end, nnz, block_rows, (const T*)data, (const I*)indices,
