@@ -146,6 +146,21 @@ NB200_API int nb200_gather(int64_t n, const void* src, const void* idx, void* ds
 NB200_API int nb200_scatter(int64_t n, const void* src, const void* idx, void* dst,
                   int dtype, int itype, nb200_stream stream);
 
+/* Structure check of a CSR pattern, run once per pattern by the host layer before kernels that would
+ * otherwise read out of bounds (column or row-pointer out of range) or return wrong results silently
+ * (the triangular solve and the SpGEMM backward rely on columns ascending within each row; a solve
+ * without `unit` divides by the stored diagonal).  The reference does not check any of this
+ * (its checks are device/dtype only, cpp/sparse_csr.cpp:125-148) and has undefined behaviour instead.
+ * Writes the OR of the NB200_CHECK_* bits that apply into the device word `flags` (0 = clean). */
+enum {
+    NB200_CHECK_BAD_INDPTR = 1,    /* indptr[0] != 0, indptr[rows] != nnz, or not non-decreasing   */
+    NB200_CHECK_COLUMN_RANGE = 2,  /* a column index outside [0, cols)                              */
+    NB200_CHECK_UNSORTED = 4,      /* columns of a row not strictly ascending (includes duplicates) */
+    NB200_CHECK_NO_DIAGONAL = 8    /* a row r < cols without a stored entry (r, r)                  */
+};
+NB200_API int nb200_csr_check(int64_t rows, int64_t cols, int64_t nnz, const void* indices, const void* indptr,
+                              int itype, int32_t* flags, nb200_stream stream);
+
 /* out32[k] = (int32) in64[k] and out64[k] = in32[k]: index-width conversion used when the host
  * layer builds its cached int32 copy of a pattern (the reference stores int64 everywhere,
  * numml/sparse/_csr.py:599-600,626-639). */

@@ -26,6 +26,7 @@ SIGNATURES = {
     "nb200_spgemv_grad_A": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _vp, _int, _int, _vp]),
     "nb200_csr_block_profile": (_int, [_i64, _vp, _int, _vp, _vp]),
     "nb200_spmv_pipeline_tile": (_int, []),
+    "nb200_csr_check": (_int, [_i64, _i64, _i64, _vp, _vp, _int, _vp, _vp]),
     "nb200_csr_transpose_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "nb200_csr_transpose_structure": (_int, [_i64, _i64, _i64, _vp, _vp, _int, _vp, _vp, _vp, _int, _vp, _sz, _vp]),
     "nb200_gather": (_int, [_i64, _vp, _vp, _vp, _int, _int, _vp]),

@@ -19,6 +19,7 @@ import torch
 from . import _cabi
 
 _INT32_MAX = 2 ** 31 - 1
+CHECK_BAD_INDPTR, CHECK_COLUMN_RANGE, CHECK_UNSORTED, CHECK_NO_DIAGONAL = 1, 2, 4, 8   # NB200_CHECK_* of the C header
 _CACHE = collections.OrderedDict()
 _CACHE_SIZE = 8
 force_int64 = False  # set True to make every kernel read the int64 arrays as stored (measurement aid)
@@ -58,6 +59,34 @@ class PatternPlan:
                 _cabi.call("nb200_narrow_indices", self.rows + 1, _ptr(self.indptr), _ptr(p32), _stream())
             self._narrow = (i32, p32)
         return self._narrow[0], self._narrow[1], _cabi.I32
+
+    # -- structure check ---------------------------------------------------------------------
+    def check_flags(self):
+        """NB200_CHECK_* bits of the pattern (0 = clean), computed once per plan by nb200_csr_check."""
+        if "check" not in self.extra:
+            if self.indices.dtype != torch.int64 or self.indptr.dtype != torch.int64:
+                raise RuntimeError("CSR index arrays must be int64 tensors")
+            dev = self.indices.device
+            with torch.cuda.device(dev):
+                flags = torch.zeros(1, dtype=torch.int32, device=dev)
+                _cabi.call("nb200_csr_check", self.rows, self.cols, self.nnz, _ptr(self.indices), _ptr(self.indptr),
+                           _cabi.I64, _ptr(flags), _stream())
+                self.extra["check"] = int(flags.item())
+        return self.extra["check"]
+
+    def require(self, sorted_columns=False, diagonal=False, what="this operation"):
+        """Raise (instead of reading out of bounds or answering wrongly, as the reference would) when
+        the pattern is malformed, or lacks a property that ``what`` relies on."""
+        flags = self.check_flags()
+        if flags & CHECK_BAD_INDPTR:
+            raise RuntimeError("malformed CSR matrix: indptr must start at 0, end at nnz and never decrease")
+        if flags & CHECK_COLUMN_RANGE:
+            raise RuntimeError(f"malformed CSR matrix: a column index lies outside [0, {self.cols})")
+        if sorted_columns and flags & CHECK_UNSORTED:
+            raise RuntimeError(f"{what} needs the column indices of every row strictly ascending "
+                               "(sorted, without duplicates)")
+        if diagonal and flags & CHECK_NO_DIAGONAL:
+            raise RuntimeError(f"{what} needs a stored diagonal entry in every row")
 
     # -- transposed structure ----------------------------------------------------------------
     def transpose(self):
@@ -152,6 +181,7 @@ def get_plan(rows, cols, indices, indptr):
         _CACHE.move_to_end(key)
         return plan
     plan = PatternPlan(rows, cols, indices, indptr)
+    plan.require()                     # row pointers and column range: nothing may index out of bounds later
     _CACHE[key] = plan
     while len(_CACHE) > _CACHE_SIZE:
         _CACHE.popitem(last=False)

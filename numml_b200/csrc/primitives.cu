@@ -287,6 +287,51 @@ extern "C" int nb200_scatter(int64_t n, const void* src, const void* idx, void* 
         (scatter_kernel<T, I><<<ew_grid(n), 256, 0, as_stream(stream)>>>(n, (const T*)src, (const I*)idx, (T*)dst), launch_status()));
 }
 
+// ---------------------------------------------------------------------------------------------
+// Structure check: finds, without faulting, what would make a kernel read out of bounds or give a
+// wrong answer silently.  One thread per row; flags are OR-ed into one device word.
+// ---------------------------------------------------------------------------------------------
+namespace nb200 {
+template <typename I>
+__global__ void csr_check_kernel(int64_t rows, int64_t cols, int64_t nnz, const I* __restrict__ indices,
+                                 const I* __restrict__ indptr, int32_t* __restrict__ flags) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    int found = 0;
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += stride) {
+        const int64_t b = (int64_t)indptr[r], e = (int64_t)indptr[r + 1];
+        if ((r == 0 && b != 0) || (r == rows - 1 && e != nnz) || b > e || b < 0 || e > nnz) {
+            found |= NB200_CHECK_BAD_INDPTR;
+            continue;                                      // the row's range cannot be trusted
+        }
+        bool diag = false;
+        int64_t prev = -1;
+        for (int64_t k = b; k < e; ++k) {
+            const int64_t c = (int64_t)indices[k];
+            if (c < 0 || c >= cols) found |= NB200_CHECK_COLUMN_RANGE;
+            if (c <= prev) found |= NB200_CHECK_UNSORTED;  // also catches duplicates
+            if (c == r) diag = true;
+            prev = c;
+        }
+        if (!diag && r < cols) found |= NB200_CHECK_NO_DIAGONAL;
+    }
+    if (found) atomicOr(flags, found);
+}
+}  // namespace nb200
+
+extern "C" int nb200_csr_check(int64_t rows, int64_t cols, int64_t nnz, const void* indices, const void* indptr,
+                               int itype, int32_t* flags, nb200_stream stream) {
+    if (rows < 0 || cols < 0 || nnz < 0 || !flags) return NB200_ERR_BAD_ARG;
+    cudaStream_t st = nb200::as_stream(stream);
+    if (cudaMemsetAsync(flags, 0, sizeof(int32_t), st) != cudaSuccess) return NB200_ERR_CUDA;
+    if (rows == 0) return NB200_OK;
+    if (!indptr || (nnz > 0 && !indices)) return NB200_ERR_BAD_ARG;
+    const int64_t want = nb200::ceil_div(rows, (int64_t)256);
+    const unsigned grid = (unsigned)(want > (int64_t)nb200::kSMs * 32 ? (int64_t)nb200::kSMs * 32 : want);
+    return NB200_DISPATCH_I(itype,
+        (nb200::csr_check_kernel<I><<<grid, 256, 0, st>>>(rows, cols, nnz, (const I*)indices, (const I*)indptr, flags),
+         nb200::launch_status()));
+}
+
 extern "C" int nb200_narrow_indices(int64_t n, const int64_t* in64, int32_t* out32, nb200_stream stream) {
     if (n < 0) return NB200_ERR_BAD_ARG;
     if (n == 0) return NB200_OK;

@@ -278,6 +278,9 @@ def spgemm_backward(grad_C, C_indices, C_indptr, A_rows, A_cols, A_data, A_indic
     C_indices, C_indptr = _index_tensor(C_indices), _index_tensor(C_indptr)
     plan_a = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
     plan_b = _plan.get_plan(B_rows, B_cols, _index_tensor(B_indices), _index_tensor(B_indptr))
+    # the gradients are found by merging sorted rows (reference cpp/sparse_csr_cpu.cpp:218-307 assumes the same)
+    plan_a.require(sorted_columns=True, what="the SpGEMM backward")
+    plan_b.require(sorted_columns=True, what="the SpGEMM backward")
     ai, ap, bi, bp, itype = _common_width(plan_a, plan_b)
     if itype == _cabi.I32:
         t_indptr, t_indices, t_perm, _ = plan_a.transpose()
@@ -355,6 +358,7 @@ def sptrsv_forward(A_rows, A_cols, A_data, A_indices, A_indptr, lower, unit, b):
     A_data = _values(A_data)
     b = _rhs(b, A_rows, A_data)
     plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
+    plan.require(sorted_columns=True, diagonal=not unit, what="the triangular solve")
     idx, ptr, itype = plan.csr()
     with _on(dev):
         order, nlevels = plan.sptrsv_order(lower)
@@ -367,6 +371,7 @@ def sptrsv_backward(grad_x, x, A_rows, A_cols, A_data, A_indices, A_indptr, lowe
     grad_x = _rhs(grad_x, A_rows, A_data)
     x = _rhs(x, A_rows, A_data)
     plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
+    plan.require(sorted_columns=True, diagonal=not unit, what="the triangular solve")
     idx, ptr, itype = plan.csr()
     nrhs = 1 if x.ndim == 1 else int(x.shape[1])
     with _on(dev):

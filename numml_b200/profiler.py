@@ -7,7 +7,8 @@
 prints, when the outermost section closes, one line per section indented by nesting depth
 (same usage and output shape as the reference's ``numml/profiler.py:4-55``).  Unlike the reference,
 the device is synchronised when a section opens and closes (``Profiler.sync``), so asynchronous
-CUDA work is charged to the section that enqueued it.
+CUDA work is charged to the section that enqueued it, and every section is also an NVTX range
+(``Profiler.nvtx``), so the same labels appear on the timeline of an attached GPU profiler.
 """
 import time
 
@@ -27,21 +28,39 @@ class _Node:
             yield from child.lines(depth + 1, width)
 
 
-def _device_barrier():
+def _cuda_live():
     import torch
-    if torch.cuda.is_available() and torch.cuda.is_initialized():
+    return torch.cuda.is_available() and torch.cuda.is_initialized()
+
+
+def _device_barrier():
+    if _cuda_live():
+        import torch
         torch.cuda.synchronize()
+
+
+def _nvtx(push, label=None):
+    if not _cuda_live():
+        return False
+    import torch
+    if push:
+        torch.cuda.nvtx.range_push(label)
+    else:
+        torch.cuda.nvtx.range_pop()
+    return True
 
 
 class Profiler:
     enabled = True      # set False to turn every section into a no-op
     sync = True         # synchronise the CUDA device at section boundaries
+    nvtx = True         # open an NVTX range per section (a no-op unless a profiler is attached)
     tab_width = 2
     current = None      # innermost open section (a _Node), or None
 
     def __init__(self, section_name):
         self.section_name = section_name
         self._node = None
+        self._ranged = False
 
     def __enter__(self):
         if Profiler.enabled:
@@ -49,6 +68,7 @@ class Profiler:
             Profiler.current = self._node
             if Profiler.sync:
                 _device_barrier()
+            self._ranged = Profiler.nvtx and _nvtx(True, self.section_name)
             self._node.t0 = time.perf_counter()
         return self
 
@@ -58,6 +78,8 @@ class Profiler:
             return False
         if Profiler.sync:
             _device_barrier()
+        if self._ranged:
+            _nvtx(False)
         node.seconds = time.perf_counter() - node.t0
         Profiler.current = node.parent
         if node.parent is None and exc_type is None:

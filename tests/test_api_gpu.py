@@ -287,3 +287,52 @@ def test_library_cg_loop_vs_oracle(sp, oracle, dtype, tol, with_x0):
     xt, ht = kry.conjugate_gradient(Ag, b.to(gpu), x=None if x0 is None else x0.to(gpu), rtol=0.0, iterations=iters)
     assert_close(xg, xt.detach(), "x (torch-op loop)", tol=tol)
     assert xt.requires_grad
+
+
+# ---------------------------------------------------------------------------------------------
+# Malformed structure raises instead of reading out of bounds or answering wrongly
+# ---------------------------------------------------------------------------------------------
+def _flags(rows, cols, indices, indptr):
+    import ctypes
+    from numml_b200 import _cabi
+    i, p = torch.tensor(indices, dtype=torch.int64).cuda(), torch.tensor(indptr, dtype=torch.int64).cuda()
+    out = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    _cabi.call("nb200_csr_check", rows, cols, i.numel(), P(i), P(p), _cabi.I64, P(out),
+               ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    return int(out.item())
+
+
+def test_structure_check_flags():
+    assert _flags(3, 3, [0, 0, 1, 2], [0, 1, 3, 4]) == 0                 # lower bidiagonal: clean
+    assert _flags(3, 3, [0, 1, 0, 2], [0, 1, 3, 4]) == 4                 # row 1 descending
+    assert _flags(3, 3, [0, 1, 1, 2], [0, 1, 3, 4]) == 4                 # duplicate column
+    assert _flags(3, 3, [0, 0, 2], [0, 1, 2, 3]) == 8                    # row 1 has no diagonal
+    assert _flags(3, 3, [0, 1, 3], [0, 1, 2, 3]) == 2 | 8                # column 3 of a 3-column matrix
+    assert _flags(3, 3, [0, 1, 2], [0, 1, 2, 2]) & 1                     # indptr ends before nnz
+    assert _flags(3, 3, [0, 1, 2], [0, 2, 1, 3]) & 1                     # indptr decreases
+    assert _flags(2, 4, [3, 0], [0, 1, 2]) == 8                          # rectangular: rows 0, 1 lack (r, r)
+    assert _flags(0, 0, [], [0]) == 0
+
+
+def test_malformed_matrices_raise():
+    import numml_b200.numml_torch_cpp as ops
+    d = torch.ones(4, dtype=torch.float64).cuda()
+    x = torch.ones(3, dtype=torch.float64).cuda()
+    L = lambda idx, ptr: (torch.tensor(idx).cuda(), torch.tensor(ptr).cuda())  # noqa: E731
+    i, p = L([0, 1, 0, 2], [0, 1, 3, 4])                                 # unsorted row
+    ops.spgemv_forward(3, 3, d, i, p, x)                                 # a product does not care
+    with pytest.raises(RuntimeError, match="strictly ascending"):
+        ops.sptrsv_forward(3, 3, d, i, p, True, False, x)
+    i, p = L([0, 0, 2], [0, 1, 2, 3])                                    # no diagonal in row 1
+    with pytest.raises(RuntimeError, match="diagonal"):
+        ops.sptrsv_forward(3, 3, d[:3], i, p, True, False, x)
+    y = ops.sptrsv_forward(3, 3, d[:3], i, p, True, True, x)             # unit diagonal: nothing stored is needed
+    assert torch.equal(y.cpu(), torch.tensor([1., 0., 1.], dtype=torch.float64))
+    i, p = L([0, 1, 3], [0, 1, 2, 3])                                    # column out of range
+    with pytest.raises(RuntimeError, match="outside"):
+        ops.spgemv_forward(3, 3, d[:3], i, p, x)
+    i, p = L([0, 1, 2], [0, 1, 2, 2])                                    # indptr does not reach nnz
+    with pytest.raises(RuntimeError, match="indptr"):
+        ops.spgemv_forward(3, 3, d[:3], i, p, x)
+    ops.check_status()

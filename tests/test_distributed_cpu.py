@@ -165,3 +165,51 @@ def test_ghost_row_extension_reproduces_the_backward():
     idx, ptr = torch.tensor([1, 1]), torch.tensor([0, 1, 2])          # entries (0,1) and (1,1): (1,0) is missing
     _, t_idx, t_ptr, t_perm = oracle.csr_transpose_forward(2, 2, torch.zeros(2, dtype=torch.float64), idx, ptr)
     assert nd.mirror_positions(idx, ptr, torch.zeros(2, dtype=torch.bool), t_ptr, t_idx, t_perm) is None
+
+
+def _leaving_worker(rank, world, init_file, out_file):
+    """Rank 1 leaves right after the rendezvous; rank 0 then starts an exchange that needs it."""
+    import datetime
+    import time
+    for p in (ROOT, os.path.join(ROOT, "oracle")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import csr_oracle as oracle
+    from numml_b200 import distributed as nd, workloads as W
+    dist.init_process_group("gloo", init_method="file://" + init_file, rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=10))
+    if rank == 1:
+        os._exit(0)                                    # gone without a word, nothing of its own in flight
+    time.sleep(1.0)
+    d, i, p, (m, n) = W.poisson3d_7pt(4, torch.float64, nz=8)
+    bounds = nd.partition_rows(m, world)
+    sl = slice(int(p[bounds[0]]), int(p[bounds[1]]))
+    t0 = time.time()
+    try:
+        A = nd.DistSparseCSR(d[sl].clone(), i[sl].clone(), p[:bounds[1] + 1].clone(), (m, n), bounds, ops=oracle)
+        A @ torch.ones(bounds[1], dtype=torch.float64)
+        outcome = "completed"
+    except Exception as e:                             # noqa: BLE001  (any error is the expected outcome)
+        outcome = "error:" + type(e).__name__
+    with open(out_file, "w") as f:
+        f.write(f"{outcome} {time.time() - t0:.1f}")
+    os._exit(0)                                        # the process group cannot be torn down cleanly
+
+
+def test_a_rank_that_leaves_ends_the_exchange_with_an_error():
+    """Failure on the host, no GPU involved: the surviving rank must get an exception from its next
+    exchange within the process-group timeout instead of waiting forever."""
+    with tempfile.TemporaryDirectory() as tmp:
+        init_file, out_file = os.path.join(tmp, "rendezvous"), os.path.join(tmp, "outcome")
+        ctx = mp.spawn(_leaving_worker, args=(2, init_file, out_file), nprocs=2, join=False)
+        import time
+        deadline = time.time() + 90
+        while not ctx.join(timeout=2):                 # join() returns as soon as any one process ends
+            if time.time() > deadline:
+                for proc in ctx.processes:
+                    if proc.is_alive():
+                        proc.kill()
+                pytest.fail("a rank was still waiting after 90 s")
+        outcome, seconds = open(out_file).read().split()
+        assert outcome.startswith("error:"), outcome
+        assert float(seconds) < 60

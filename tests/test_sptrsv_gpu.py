@@ -50,15 +50,16 @@ def test_random_vs_oracle(oracle, ops, dtype, lower, unit, n, density):
     assert_same(gA_ref, gA, "grad_A")
 
 
-def test_missing_diagonal_entries_follow_the_reference(oracle, ops):
-    """With `unit` the diagonal need not be stored at all; without it a missing diagonal divides
-    by zero exactly like the reference (inf / nan), it never stalls."""
+def test_missing_diagonal_entries(oracle, ops):
+    """With `unit` the diagonal need not be stored at all (same result as the reference); without
+    `unit` a row that stores no diagonal is refused by the structure check before any kernel runs
+    (the reference divides by an uninitialised value there)."""
     d, i, p, _ = W.random_triangular(50, 0.2, lower=True, seed=3, dtype=torch.float64, with_diag=False)
     b = W.randn(50, 1, torch.float64)
     x_ref = oracle.sptrsv_forward(50, 50, d, i, p, True, True, b)
     assert_same(x_ref, ops.sptrsv_forward(50, 50, d.cuda(), i.cuda(), p.cuda(), True, True, b.cuda()), "unit, no diagonal")
-    x_bad = ops.sptrsv_forward(50, 50, d.cuda(), i.cuda(), p.cuda(), True, False, b.cuda())
-    assert not torch.isfinite(x_bad).all()
+    with pytest.raises(RuntimeError, match="diagonal"):
+        ops.sptrsv_forward(50, 50, d.cuda(), i.cuda(), p.cuda(), True, False, b.cuda())
 
 
 @pytest.mark.parametrize("nrhs", [1, 2, 3, 16, 40])
