@@ -12,7 +12,8 @@ with one exchange step per operator:
     sent back to their owners and added in a fixed peer order (deterministic).
   * SpGEMM: the rows of B that a rank's columns refer to are fetched from their owners (row
     lengths, then indices and values); the local product's rows concatenate to the single-device
-    result bit for bit, since output rows are independent.
+    result bit for bit, since output rows are independent.  Backward: grad_A is local; gradients
+    of fetched rows of B are sent back to their owners and added there.
 
 All exchanges are grouped ``isend`` / ``irecv`` calls (NCCL over NVLink on GPUs, gloo on CPU);
 the local compute goes through an operator module with the reference's function names
@@ -239,25 +240,27 @@ def dist_conjugate_gradient(A, b_local, iterations, x_local=None):
     return x, torch.stack(hist)
 
 
-def _fetch_rows(A, B):
+def _fetch_rows(A, B, B_data):
     """CSR of the rows of B that A's halo columns refer to, fetched from their owners.
-    Returns (data, indices[global cols], indptr) with one row per halo slot of A."""
+    Returns (data, indices[global cols], indptr) with one row per halo slot of A, and for every peer
+    that was served the positions in this rank's B arrays of the entries sent to it."""
     halo = A.halo
-    dev = B.data.device
+    dev = B_data.device
     lens_local = (B.indptr[1:] - B.indptr[:-1])
     lens_ext = halo.extend(lens_local)                       # row lengths of [local | halo] rows
     halo_lens = lens_ext[halo.n_local:]
     indptr = torch.zeros(halo.n_halo + 1, dtype=torch.int64, device=dev)
     indptr[1:] = torch.cumsum(halo_lens, 0)
     total = int(indptr[-1])
-    data = torch.empty(total, dtype=B.data.dtype, device=dev)
+    data = torch.empty(total, dtype=B_data.dtype, device=dev)
     indices = torch.empty(total, dtype=torch.int64, device=dev)
-    ops, keep = [], []
+    ops, keep, sent_pos = [], [], {}
     for p in halo.peers_out:                                 # rows of mine that rank p needs
         rows = halo.send[p]
         starts, cnts = B.indptr[rows], lens_local[rows]
         pos = torch.repeat_interleave(starts - torch.cumsum(cnts, 0) + cnts, cnts) + torch.arange(int(cnts.sum()), device=dev)
-        v, c = B.data.detach()[pos].contiguous(), B.global_indices[pos].contiguous()
+        sent_pos[p] = pos
+        v, c = B_data[pos].contiguous(), B.global_indices[pos].contiguous()
         keep += [v, c]
         if v.numel() > 0:
             ops.append(dist.P2POp(dist.isend, v, halo._peer(p), group=halo.group))
@@ -268,21 +271,67 @@ def _fetch_rows(A, B):
             ops.append(dist.P2POp(dist.irecv, data[a:b], halo._peer(p), group=halo.group))
             ops.append(dist.P2POp(dist.irecv, indices[a:b], halo._peer(p), group=halo.group))
     HaloPlan._run(ops)
-    return data, indices, indptr
+    return data, indices, indptr, sent_pos
+
+
+class _DistSpGEMM(torch.autograd.Function):
+    """C = A B on row blocks.  Forward: the rows of B that this rank's columns refer to are fetched
+    from their owners and the local product is formed against ``[B_local ; fetched rows]``.
+    Backward: the local SpGEMM backward gives grad_A (local) and a gradient for every entry of the
+    extended B; the part that belongs to fetched rows travels back to the owners, who add it to
+    their own in ascending peer order (reproducible)."""
+
+    @staticmethod
+    def forward(ctx, A, B, A_data, B_data):
+        halo = A.halo
+        B_values = B_data.detach()
+        h_data, h_indices, h_indptr, sent_pos = _fetch_rows(A, B, B_values)
+        n_ext = halo.n_local + halo.n_halo
+        ext_data = torch.cat((B_values, h_data))
+        ext_indices = torch.cat((B.global_indices, h_indices))
+        ext_indptr = torch.cat((B.indptr, h_indptr[1:] + B.indptr[-1]))
+        C_data, C_indices, C_indptr = A.ops.spgemm_forward(A.n_rows, n_ext, A_data.detach(), A.indices, A.indptr,
+                                                           n_ext, B.global_shape[1], ext_data, ext_indices, ext_indptr)
+        ctx.A, ctx.B = A, B
+        ctx.sent_pos, ctx.h_indptr = sent_pos, h_indptr
+        ctx.save_for_backward(A_data, ext_data, ext_indices, ext_indptr, C_indices, C_indptr)
+        ctx.mark_non_differentiable(C_indices, C_indptr)
+        return C_data, C_indices, C_indptr
+
+    @staticmethod
+    def backward(ctx, grad_C, _grad_indices, _grad_indptr):
+        A, B = ctx.A, ctx.B
+        halo = A.halo
+        A_data, ext_data, ext_indices, ext_indptr, C_indices, C_indptr = ctx.saved_tensors
+        n_ext = halo.n_local + halo.n_halo
+        grad_A, grad_ext = A.ops.spgemm_backward(grad_C.contiguous(), C_indices, C_indptr,
+                                                 A.n_rows, n_ext, A_data.detach(), A.indices, A.indptr,
+                                                 n_ext, B.global_shape[1], ext_data, ext_indices, ext_indptr)
+        nb = int(B.indptr[-1])
+        grad_B = grad_ext[:nb].clone()
+        ops, bufs = [], {}
+        for p in halo.peers_in:                              # gradients of the rows fetched from p go home
+            a = int(ctx.h_indptr[halo.recv_offsets[p]])
+            b = int(ctx.h_indptr[halo.recv_offsets[p] + halo.recv_counts[p]])
+            if b > a:
+                ops.append(dist.P2POp(dist.isend, grad_ext[nb + a:nb + b].contiguous(), halo._peer(p), group=halo.group))
+        for p in halo.peers_out:
+            count = int(ctx.sent_pos[p].numel())
+            if count > 0:
+                bufs[p] = torch.empty(count, dtype=grad_ext.dtype, device=grad_ext.device)
+                ops.append(dist.P2POp(dist.irecv, bufs[p], halo._peer(p), group=halo.group))
+        HaloPlan._run(ops)
+        for p in sorted(bufs):
+            grad_B.index_add_(0, ctx.sent_pos[p], bufs[p])
+        return None, None, grad_A, grad_B
 
 
 def dist_spgemm(A, B):
     """This rank's rows of C = A B for row-partitioned A (columns partitioned like B's rows) and B.
-    Returns ``(C_data, C_indices[global cols], C_indptr)``; the blocks of all ranks concatenate
-    to the single-device product.  Forward only (no autograd through the exchange)."""
-    halo = A.halo
-    h_data, h_indices, h_indptr = _fetch_rows(A, B)
-    n_ext = halo.n_local + halo.n_halo
-    ext_data = torch.cat((B.data.detach(), h_data))
-    ext_indices = torch.cat((B.global_indices, h_indices))
-    ext_indptr = torch.cat((B.indptr, h_indptr[1:] + B.indptr[-1]))
-    return A.ops.spgemm_forward(A.n_rows, n_ext, A.data.detach(), A.indices, A.indptr,
-                                n_ext, B.global_shape[1], ext_data, ext_indices, ext_indptr)
+    Returns ``(C_data, C_indices[global cols], C_indptr)``; the blocks of all ranks concatenate to
+    the single-device product.  ``C_data`` is differentiable with respect to the stored values of
+    both factors (every rank must then take part in the backward pass, which exchanges)."""
+    return _DistSpGEMM.apply(A, B, A.data, B.data)
 
 
 def ghost_row_extension(indices, indptr, n_local, n_ext):

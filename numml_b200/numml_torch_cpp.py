@@ -278,8 +278,8 @@ def spgemm_backward(grad_C, C_indices, C_indptr, A_rows, A_cols, A_data, A_indic
     C_indices, C_indptr = _index_tensor(C_indices), _index_tensor(C_indptr)
     plan_a = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
     plan_b = _plan.get_plan(B_rows, B_cols, _index_tensor(B_indices), _index_tensor(B_indptr))
-    # the gradients are found by merging sorted rows (reference cpp/sparse_csr_cpu.cpp:218-307 assumes the same)
-    plan_a.require(sorted_columns=True, what="the SpGEMM backward")
+    # the gradients are found by merging / searching the sorted rows of B and C (the reference,
+    # cpp/sparse_csr_cpu.cpp:218-307, assumes the same); the order of the entries within a row of A is free
     plan_b.require(sorted_columns=True, what="the SpGEMM backward")
     ai, ap, bi, bp, itype = _common_width(plan_a, plan_b)
     if itype == _cabi.I32:

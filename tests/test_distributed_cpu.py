@@ -65,6 +65,18 @@ def _worker(rank, world, init_file, case):
         assert torch.equal(Ci, C_ref[1][a:b])
         assert torch.allclose(Cd, C_ref[0][a:b], rtol=1e-13, atol=1e-13)
 
+        # ---- SpGEMM backward: grad_A local, grad_B of fetched rows sent home and added ---------
+        gC = W.randn(C_ref[0].numel(), 6, torch.float64)
+        gA3_ref, gB3_ref = oracle.spgemm_backward(gC, C_ref[1], C_ref[2], m, n, d, i, p, m, n, d, i, p)
+        Bm = nd.DistSparseCSR(d[sl].clone(), i[sl].clone(), (p[lo:hi + 1] - p[lo]).clone(), (m, n), bounds, ops=oracle)
+        Bm.requires_grad = True
+        A.data.grad = None
+        Cd2, _, _ = A @ Bm
+        assert torch.equal(Cd2.detach(), Cd.detach())
+        Cd2.backward(gC[a:b])
+        assert torch.allclose(A.data.grad, gA3_ref[sl], rtol=1e-13, atol=1e-13)
+        assert torch.allclose(Bm.data.grad, gB3_ref[sl], rtol=1e-12, atol=1e-13)
+
         # ---- CG with all-reduced dots (SPD case only) -----------------------------------------
         if case == "stencil":
             import numpy as np
