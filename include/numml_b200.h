@@ -105,7 +105,9 @@ NB200_API int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
  * transpose (so t_indptr == indptr, t_indices == indices and only t_perm is needed), restricted to
  * rows [row_begin, row_end): grad_A[k] for the entries of those rows and grad_x[i] for those i.
  * Every pointer is the base of its array (absolute indexing).  Used by the row-partitioned driver,
- * which runs the rows feeding its exchange first.  Needs block_rows in 1..256 as described above. */
+ * which runs the rows feeding its exchange first.  Needs block_rows in 1..256 as described above and
+ * `indices`, `t_perm`, `grad_A` 16-byte aligned (bulk copies of the index streams, two-entry vector
+ * stores of grad_A); NB200_ERR_ALIGN otherwise. */
 NB200_API int nb200_spgemv_backward_symmetric_rows(int64_t n, int64_t nnz, int64_t row_begin, int64_t row_end,
                                                    const void* data, const void* indices, const void* indptr,
                                                    const void* t_perm, const void* x, const void* g,
