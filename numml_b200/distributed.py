@@ -334,6 +334,15 @@ def dist_spgemm(A, B):
     return _DistSpGEMM.apply(A, B, A.data, B.data)
 
 
+def rows_with_halo_columns(indices, indptr, n_local):
+    """Boolean mask over the rows of a block in ``[local | halo]`` numbering: True where the row
+    stores at least one entry in a halo column (>= n_local).  Empty rows, leading ones included,
+    are False."""
+    running = torch.zeros(int(indices.numel()) + 1, dtype=torch.int64, device=indices.device)
+    torch.cumsum((indices >= n_local).to(torch.int64), 0, out=running[1:])
+    return (running[indptr[1:]] - running[indptr[:-1]]) > 0
+
+
 def ghost_row_extension(indices, indptr, n_local, n_ext):
     """Square, pattern-symmetric extension of a rank's block of rows.
 
@@ -414,9 +423,7 @@ class DistSpMVEngine:
         self.esize = self.ptr.element_size()
         self.vsize = A.data.element_size()
         # rows that reference no halo column, as one contiguous range aligned to the kernel's row blocks
-        counts = torch.zeros(self.n + 1, dtype=torch.int64, device=dev)
-        counts[1:] = torch.cumsum((A.indices >= halo.n_local).to(torch.int64), 0)[A.indptr[1:] - 1] if self.nnz else 0
-        has_halo = (counts[1:] - counts[:-1]) > 0 if self.nnz else torch.zeros(self.n, dtype=torch.bool, device=dev)
+        has_halo = rows_with_halo_columns(A.indices, A.indptr, halo.n_local)
         marks = [-1] + torch.nonzero(has_halo).flatten().tolist() + [self.n]
         gaps = [(marks[q + 1] - marks[q] - 1, marks[q] + 1, marks[q + 1]) for q in range(len(marks) - 1)]
         _, a, b = max(gaps)

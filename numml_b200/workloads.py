@@ -23,40 +23,38 @@ def _stencil(dims, offsets, diag_val, off_val, dtype, lower_only=False, row_rang
     offsets   : list of index-offset tuples, excluding the centre
     row_range : (lo, hi) builds only rows lo..hi-1 (columns stay global); the returned shape is
                 (hi - lo, number of grid points)
+
+    The entries of a row are laid out in ascending order of their column offset, so masking out
+    the neighbours that fall off the grid leaves every row sorted without a sort.
     """
     dims = tuple(int(d) for d in dims)
     ntot = int(np.prod(dims))
     lo, hi = (0, ntot) if row_range is None else (int(row_range[0]), int(row_range[1]))
-    ids = np.arange(lo, hi, dtype=np.int64)
     n = hi - lo
-    coords = np.unravel_index(ids, dims)
     strides = [int(np.prod(dims[k + 1:])) for k in range(len(dims))]
-    cols = [ids]
-    vals = [np.full(n, diag_val, dtype=np.float64)]
-    valid = [np.ones(n, dtype=bool)]
+    ids = torch.arange(lo, hi, dtype=torch.int64)
+    coords = [((ids // strides[k]) % dims[k]).to(torch.int32) for k in range(len(dims))]
+    entries = [(0, None, diag_val)]
     for off in offsets:
-        ok = np.ones(n, dtype=bool)
-        delta = 0
-        for k, o in enumerate(off):
-            c = coords[k] + o
-            ok &= (c >= 0) & (c < dims[k])
-            delta += o * strides[k]
+        delta = sum(o * s for o, s in zip(off, strides))
         if lower_only and delta > 0:
             continue
-        cols.append(ids + delta)
-        vals.append(np.full(n, off_val, dtype=np.float64))
-        valid.append(ok)
-    cols = np.stack(cols, axis=1)
-    vals = np.stack(vals, axis=1)
-    valid = np.stack(valid, axis=1)
-    order = np.argsort(np.where(valid, cols, np.iinfo(np.int64).max), axis=1, kind="stable")
-    cols = np.take_along_axis(cols, order, axis=1)
-    vals = np.take_along_axis(vals, order, axis=1)
-    valid = np.take_along_axis(valid, order, axis=1)
-    counts = valid.sum(axis=1)
-    indptr = np.zeros(n + 1, dtype=np.int64)
-    np.cumsum(counts, out=indptr[1:])
-    return _pack(vals[valid], cols[valid], indptr, (n, ntot), dtype)
+        entries.append((delta, off, off_val))
+    entries.sort(key=lambda e: e[0])
+    valid = torch.ones((n, len(entries)), dtype=torch.bool)
+    for q, (_, off, _) in enumerate(entries):
+        for k, o in enumerate(off or ()):
+            if o > 0:
+                valid[:, q] &= coords[k] < dims[k] - o
+            elif o < 0:
+                valid[:, q] &= coords[k] >= -o
+    indptr = torch.zeros(n + 1, dtype=torch.int64)
+    torch.cumsum(valid.sum(dim=1), 0, out=indptr[1:])
+    deltas = torch.tensor([e[0] for e in entries], dtype=torch.int64)
+    row_vals = torch.tensor([e[2] for e in entries], dtype=dtype)
+    cols = (ids[:, None] + deltas[None, :])[valid]
+    vals = row_vals.expand(n, len(entries))[valid]
+    return vals.contiguous(), cols.contiguous(), indptr, (n, ntot)
 
 
 def poisson2d_5pt(n, dtype=torch.float32):

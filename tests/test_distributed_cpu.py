@@ -124,6 +124,22 @@ def test_partition_rows():
     assert abs(int(indptr[b[1]]) - 100) <= 3
 
 
+def test_rows_with_halo_columns_handles_empty_rows():
+    """Rows are classified by their own entries only: empty rows (leading, middle, trailing) hold no
+    halo column, and the first non-empty row after them is not confused with the running total."""
+    sys.path.insert(0, ROOT)
+    from numml_b200 import distributed as nd
+    nl = 3
+    ptr = torch.tensor([0, 0, 2, 3], dtype=torch.int64)
+    idx = torch.tensor([0, 5, 1], dtype=torch.int64)
+    assert nd.rows_with_halo_columns(idx, ptr, nl).tolist() == [False, True, False]
+    ptr = torch.tensor([0, 0, 0, 1, 1, 3, 3], dtype=torch.int64)
+    idx = torch.tensor([2, 1, 4], dtype=torch.int64)
+    assert nd.rows_with_halo_columns(idx, ptr, nl).tolist() == [False, False, False, False, True, False]
+    ptr = torch.zeros(4, dtype=torch.int64)
+    assert nd.rows_with_halo_columns(torch.zeros(0, dtype=torch.int64), ptr, nl).tolist() == [False] * 3
+
+
 def test_ghost_row_extension_reproduces_the_backward():
     """The index logic behind the one-pass distributed backward, emulated on CPU: for each of two
     row blocks of a 3-D stencil, build the ghost-row extension and the mirror positions (transposed
