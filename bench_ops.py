@@ -1,7 +1,7 @@
 """Per-operator measurements for the five benchmark configurations, with the reference CPU path
 timed beside each one.
 
-    python -m numml_b200.benchmarks [--configs 1,2,3,4,5] [--no-cpu]        (6 = one GCN layer on the C3 graph)
+    python bench_ops.py [--configs 1,2,3,4,5] [--no-cpu]        (6 = one GCN layer on the C3 graph)
 
 Prints a Markdown table: CUDA-event time of each operator through the operator functions (plan
 cached, median of the repetitions), its algorithmic bytes and effective bandwidth as a fraction of
@@ -19,7 +19,7 @@ import time
 
 import torch
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 
 
 def peak_gbs():

@@ -14,7 +14,8 @@
  *   - all pointers are device pointers on the current device unless stated otherwise; data,
  *     indices and the nnz-sized outputs must be 16-byte aligned (128-bit loads and stores);
  *   - inputs are borrowed and never written; outputs and workspaces are caller-allocated, the
- *     library allocates no device memory; every call is asynchronous on `stream`;
+ *     library allocates no device memory (the one exception, at set-up time, is nb200_ipc_alloc);
+ *     every call is asynchronous on `stream`;
  *   - columns within a row are expected in ascending order wherever the reference expects it
  *     (SpGEMM backward, triangular solve).
  */
@@ -89,10 +90,16 @@ NB200_API int nb200_spmv_pipeline_tile(void);
  * three t_* pointers NULL grad_x is zeroed and accumulated with floating-point atomics in one
  * fused pass over A (order of additions not fixed).  `block_rows` / `t_block_rows` choose the
  * kernel for the pass over A / over A^T as in nb200_spgemv_forward (0 = streaming kernels).
- * `pattern_symmetric` != 0 asserts that the pattern equals its transpose (t_indptr == indptr,
- * t_indices == indices); with block_rows > 0 both gradients then come from ONE pipelined pass
- * that reads indices and t_perm once (same results, bit for bit).
+ * `pattern_symmetric` is a set of NB200_SYMMETRIC_* bits.  NB200_SYMMETRIC_PATTERN asserts that the
+ * pattern equals its transpose (t_indptr == indptr, t_indices == indices); with block_rows > 0 both
+ * gradients then come from ONE pipelined pass that reads indices and t_perm once (same results, bit
+ * for bit).  NB200_SYMMETRIC_VALUES (only together with the former) asserts in addition that the
+ * values do: data[t_perm[k]] == data[k] for every k, which nb200_csr_values_symmetric establishes.
+ * The pass then streams `data` and never reads t_perm: its traffic is exactly A, x, g and the two
+ * outputs.  The results are again the same bit for bit, because the transposed value the pass would
+ * have gathered is the entry's own.
  * ------------------------------------------------------------------------------------------- */
+enum { NB200_SYMMETRIC_PATTERN = 1, NB200_SYMMETRIC_VALUES = 2 };
 NB200_API int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
                           const void* data, const void* indices, const void* indptr,
                           const void* x, const void* g,
@@ -105,14 +112,21 @@ NB200_API int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
  * transpose (so t_indptr == indptr, t_indices == indices and only t_perm is needed), restricted to
  * rows [row_begin, row_end): grad_A[k] for the entries of those rows and grad_x[i] for those i.
  * Every pointer is the base of its array (absolute indexing).  Used by the row-partitioned driver,
- * which runs the rows feeding its exchange first.  Needs block_rows in 1..256 as described above and
- * `indices`, `t_perm`, `grad_A` 16-byte aligned (bulk copies of the index streams, two-entry vector
- * stores of grad_A); NB200_ERR_ALIGN otherwise. */
+ * which runs the rows feeding its exchange first.  `values_symmetric` != 0: data[t_perm[k]] == data[k]
+ * holds for every entry k of the rows in the range (see NB200_SYMMETRIC_VALUES above).  Needs block_rows
+ * in 1..256 as described above and `data`, `indices`, `t_perm`, `grad_A` 16-byte aligned (bulk copies of
+ * the streams, two-entry vector stores of grad_A); NB200_ERR_ALIGN otherwise. */
 NB200_API int nb200_spgemv_backward_symmetric_rows(int64_t n, int64_t nnz, int64_t row_begin, int64_t row_end,
                                                    const void* data, const void* indices, const void* indptr,
                                                    const void* t_perm, const void* x, const void* g,
-                                                   void* grad_A, void* grad_x, int block_rows, int32_t* status,
-                                                   int dtype, int itype, nb200_stream stream);
+                                                   void* grad_A, void* grad_x, int values_symmetric, int block_rows,
+                                                   int32_t* status, int dtype, int itype, nb200_stream stream);
+
+/* OR-s 1 into the device word `mismatch` (zeroed by the caller) if data[t_perm[k]] != data[k], compared
+ * as bit patterns, for some k < nnz: the test behind NB200_SYMMETRIC_VALUES.  The reference has no
+ * counterpart; its backward (cpp/sparse_csr_cpu.cpp:41-77) always walks the values it is given. */
+NB200_API int nb200_csr_values_symmetric(int64_t nnz, const void* data, const void* t_perm, int32_t* mismatch,
+                                         int dtype, int itype, nb200_stream stream);
 
 /* grad_A[k] = g[row(k)] * x[col(k)] alone: the masked outer product of spgemv_backward (reference
  * cpp/sparse_csr_cpu.cpp:59-65, cuda_kernel_masked_outerproduct cpp/sparse_csr_cuda.cu:76-95), for
@@ -201,21 +215,27 @@ NB200_API int nb200_spdmm_backward_grad_A(int64_t rows, int64_t cols, int64_t K,
  *
  *   1. nb200_spgemm_plan      counts the products of every row of A, bins the rows and writes a
  *                             header of 16 int64 words at the start of `workspace`:
- *                             [0..3] rows per bin, [4] spill slots needed by the symbolic phase,
- *                             [5] largest product count of a row.
- *   2. nb200_spgemm_symbolic  counts the distinct columns of every row of C with per-bin hash
- *                             tables (shared memory; rows with more than 4096 products use
- *                             `spill`, an array of `spill_slots` uint32), writes C_indptr
- *                             (int64, A_rows+1 entries) and extends the header: [8..11] rows per
- *                             bin for the numeric phase, [12] its spill slots, [13] nnz(C),
- *                             [14] non-zero if a spill area was too small.
+ *                             [0..4] rows per bin, [5] spill slots needed by the symbolic phase,
+ *                             [6] largest product count of a row.
+ *   2. nb200_spgemm_symbolic  counts the distinct columns of every row of C (rows with at most 32
+ *                             products: one warp per row, no table; larger rows: per-bin hash tables
+ *                             in shared memory; rows with more than 4096 products use `spill`, an
+ *                             array of `spill_slots` uint32), writes C_indptr (int64, A_rows+1
+ *                             entries) and extends the header: [8..12] rows per bin for the numeric
+ *                             phase, [13] its spill slots, [14] nnz(C), [15] non-zero if a spill area
+ *                             was too small (its rows are then skipped, nothing is written out of
+ *                             bounds).
  *   3. nb200_spgemm_numeric   fills C_indices (int64, ascending within a row) and C_data;
  *                             `spill` must hold spill_slots * (sizeof(value) + 4) bytes.
  *
- * The caller reads the header (a device-to-host copy of 128 bytes) after steps 1 and 2 to size
- * the spill areas and the outputs.  C's pattern is purely structural: numerically cancelled
- * entries are stored as zeros, like the reference's.  C_indptr / C_indices are bit-identical to
- * the reference's; values are accumulated with atomics (order not fixed).
+ * The caller reads the header (a device-to-host copy of 128 bytes) after step 2 to size the outputs
+ * and the numeric spill area.  Steps 1 and 2 can be enqueued together with spill_slots = 0: only if
+ * header[5] then turns out non-zero (a row with more than 4096 products exists) must both be repeated
+ * with a spill area of that many slots.  C's pattern is purely structural: numerically cancelled
+ * entries are stored as zeros, like the reference's.  C_indptr / C_indices are bit-identical to the
+ * reference's.  Values of rows with at most 32 products (and at most 32 entries in the row of A) are
+ * summed in the reference's order with unfused multiply and add: bit-identical to its CPU loop and
+ * reproducible; values of larger rows are accumulated with atomics (order not fixed, within tolerance).
  * `workspace` must hold nb200_spgemm_workspace_bytes(A_rows) bytes and be kept between the calls.
  * ------------------------------------------------------------------------------------------- */
 NB200_API size_t nb200_spgemm_workspace_bytes(int64_t A_rows);
@@ -348,6 +368,57 @@ NB200_API int nb200_cg_fixed_iterations(int64_t n, int64_t nnz, const void* data
                                         int block_rows, const void* b, void* x, int has_x0, void* residual_history,
                                         int64_t iterations, void* workspace, size_t workspace_bytes, int32_t* status,
                                         int dtype, int itype, nb200_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Halo exchange of a row-partitioned SpMV over peer memory.  No counterpart in the reference, which has
+ * no multi-device path (its operators take whole matrices on one device, cpp/sparse_csr.hpp:32-105).
+ *
+ * Every rank (one process per GPU) owns an exchange buffer that its neighbours map with CUDA IPC; a rank
+ * writes only its own buffer and reads only its neighbours', with ordinary stores and loads over NVLink.
+ * An exchange buffer holds flag words and packed areas; a packed area has two halves of `count`
+ * elements, used alternately by even and odd steps.
+ *
+ * nb200_halo_publish   area[step & 1][k] = src[idx ? idx[k] : k] for k < count, then the flag word is set
+ *                      to the step number (release, system scope).  `step_word` is a device word of the
+ *                      caller holding the number of the current step; with `bump_step` != 0 the call
+ *                      first advances it by one (the first publish of a step does that).  `arrivals` is a
+ *                      zeroed device word used to find the last block.
+ * nb200_halo_pull      for each of `npeers` neighbours, described by 8 int64 words each
+ *                      ([0] address of its packed area, [1] elements per half, [2] first element of this
+ *                      rank's segment, [3] elements in it, [4] first destination element in `dst`,
+ *                      [5] address of its flag word): wait until the flag has reached the current step,
+ *                      then dst[[4] + k] = area[step & 1][[2] + k].  `largest_segment` sizes the grid.
+ * nb200_halo_pull_add  for gradients: target j (an index into `grad`) receives the elements
+ *                      source_elem[c] of the packed areas of neighbours source_peer[c] (an index into the
+ *                      descriptors), c in [target_ptr[j], target_ptr[j+1]), added to grad[target[j]] in
+ *                      that order; the caller sorts them by neighbour, which makes the sum reproducible.
+ *
+ * Waits are bounded: after `wait_budget_cycles` SM cycles (<= 0: 4e9, about two seconds) without the
+ * flag arriving, NB200_ERR_WAIT_BUDGET is stored into the device word `status` and the kernel returns
+ * without copying.  The two halves make the scheme safe without acknowledgements provided every rank
+ * that reads a neighbour is read by that neighbour too (true for patterns that equal their transpose):
+ * a rank reaches the publish of step t only after its pull of step t-1 has seen every neighbour's flag
+ * at t-1, and a neighbour raises that flag only after its own pull of step t-2 has finished.
+ *
+ * nb200_ipc_alloc / nb200_ipc_open / nb200_ipc_close / nb200_ipc_free create an exchange buffer (zeroed,
+ * from cudaMalloc, since memory that other processes map cannot come out of a caching allocator's
+ * segment; this is the only allocation the library ever makes, at set-up time), export it as 64 opaque
+ * bytes, map a neighbour's buffer into this process with the calling thread's current device as the
+ * device that will access it, and undo both.  These four calls synchronise.
+ * ------------------------------------------------------------------------------------------- */
+NB200_API int nb200_halo_publish(int64_t count, const void* src, const int64_t* idx, void* area, int32_t* flag,
+                                 int32_t* step_word, int bump_step, uint32_t* arrivals, int dtype, nb200_stream stream);
+NB200_API int nb200_halo_pull(int npeers, const int64_t* desc, int64_t largest_segment, void* dst,
+                              const int32_t* step_word, int32_t* status, int64_t wait_budget_cycles,
+                              int dtype, nb200_stream stream);
+NB200_API int nb200_halo_pull_add(int npeers, const int64_t* desc, int64_t ntargets, const int64_t* target,
+                                  const int64_t* target_ptr, const int32_t* source_peer, const int64_t* source_elem,
+                                  void* grad, const int32_t* step_word, int32_t* status, int64_t wait_budget_cycles,
+                                  int dtype, nb200_stream stream);
+NB200_API int nb200_ipc_alloc(size_t bytes, void** ptr, void* handle64);
+NB200_API int nb200_ipc_open(const void* handle64, void** ptr);
+NB200_API int nb200_ipc_close(void* ptr);
+NB200_API int nb200_ipc_free(void* ptr);
 
 #ifdef __cplusplus
 }

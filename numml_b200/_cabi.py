@@ -21,8 +21,9 @@ SIGNATURES = {
     "nb200_spgemv_forward": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp, _int, _int, _vp]),
     "nb200_spgemv_backward": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _int,
                                      _vp, _int, _int, _vp]),
-    "nb200_spgemv_backward_symmetric_rows": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int,
+    "nb200_spgemv_backward_symmetric_rows": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int,
                                                     _vp, _int, _int, _vp]),
+    "nb200_csr_values_symmetric": (_int, [_i64, _vp, _vp, _vp, _int, _int, _vp]),
     "nb200_spgemv_grad_A": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _vp, _int, _int, _vp]),
     "nb200_csr_block_profile": (_int, [_i64, _vp, _int, _vp, _vp]),
     "nb200_spmv_pipeline_tile": (_int, []),
@@ -52,6 +53,13 @@ SIGNATURES = {
     "nb200_cg_fixed_iterations": (_int, [_i64, _i64, _vp, _vp, _vp, _int, _vp, _vp, _int, _vp, _i64, _vp, _sz, _vp,
                                          _int, _int, _vp]),
     "nb200_masked_outer": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _c.c_double, _vp, _int, _int, _vp]),
+    "nb200_halo_publish": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _int, _vp, _int, _vp]),
+    "nb200_halo_pull": (_int, [_int, _vp, _i64, _vp, _vp, _vp, _i64, _int, _vp]),
+    "nb200_halo_pull_add": (_int, [_int, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp]),
+    "nb200_ipc_alloc": (_int, [_sz, _c.POINTER(_vp), _vp]),
+    "nb200_ipc_open": (_int, [_vp, _c.POINTER(_vp)]),
+    "nb200_ipc_close": (_int, [_vp]),
+    "nb200_ipc_free": (_int, [_vp]),
     "nb200_spdmm_backward_grad_A": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
 }
 

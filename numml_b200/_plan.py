@@ -108,6 +108,34 @@ class PatternPlan:
             self.extra["symmetric"] = ok
         return self.extra["symmetric"]
 
+    def values_symmetric(self, data):
+        """True once ``data`` is known to equal its transpose bit for bit (``data[t_perm[k]] == data[k]``)
+        on this pattern, which must be symmetric.  The one-pass SpMV backward then streams the values
+        instead of gathering their mirror images.
+
+        The test costs a pass over the matrix and a host read of one word, so it is made only for
+        values that come back: the first call with a given tensor version answers False and remembers
+        the version; a second call with the same version runs the test and caches its answer until the
+        tensor is modified in place (torch bumps its version counter) or replaced.  Values that change
+        every step therefore never pay for it.  Writes that bypass the version counter (``.data``
+        views) are not seen, as with autograd's own saved-tensor checks."""
+        key = (data.data_ptr(), data._version, int(data.numel()), data.dtype)
+        seen = self.extra.get("values_symmetric")
+        if seen is not None and seen[0] == key:
+            if seen[1] is None:
+                _, _, t_perm, itype = self.transpose()
+                dev = data.device
+                with torch.cuda.device(dev):
+                    word = torch.zeros(1, dtype=torch.int32, device=dev)
+                    _cabi.call("nb200_csr_values_symmetric", self.nnz, _ptr(data), _ptr(t_perm), _ptr(word),
+                               _cabi.F64 if data.dtype == torch.float64 else _cabi.F32, itype, _stream())
+                    seen = (key, int(word.item()) == 0, data)
+                self.extra["values_symmetric"] = seen
+            return seen[1]
+        # keep the tensor alive so that its address cannot be reused by other values under the same key
+        self.extra["values_symmetric"] = (key, None, data)
+        return False
+
     # -- kernel choice for SpMV ---------------------------------------------------------------------
     def spmv_block_rows(self, transposed=False):
         """Rows per block for the TMA-pipelined SpMV kernels over this pattern (or over its

@@ -90,7 +90,10 @@ template <typename T>
 __global__ void __launch_bounds__(kCgThreads)
 cg_update_kernel(int64_t n, int it, const T* __restrict__ p, const T* __restrict__ Ap, T* __restrict__ x,
                  T* __restrict__ r, double* partials, unsigned* counter, CgScalars* sc, T* __restrict__ hist) {
-    const T alpha = (T)(sc->rz[it & 1] / sc->pAp);
+    // an exactly zero residual means the solve has converged (the reference's loop stops there): the
+    // remaining iterations must leave x and r as they are instead of forming 0 / 0
+    const double rz_now = sc->rz[it & 1];
+    const T alpha = rz_now == 0.0 ? (T)0 : (T)(rz_now / sc->pAp);
     double s = 0;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -109,7 +112,8 @@ cg_update_kernel(int64_t n, int it, const T* __restrict__ p, const T* __restrict
 template <typename T>
 __global__ void __launch_bounds__(kCgThreads)
 cg_direction_kernel(int64_t n, int it, const T* __restrict__ r, T* __restrict__ p, const CgScalars* sc) {
-    const T beta = (T)(sc->rz[(it + 1) & 1] / sc->rz[it & 1]);
+    const double rz_old = sc->rz[it & 1];
+    const T beta = rz_old == 0.0 ? (T)0 : (T)(sc->rz[(it + 1) & 1] / rz_old);
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = r[i] + beta * p[i];
 }

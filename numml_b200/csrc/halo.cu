@@ -1,0 +1,218 @@
+// Halo exchange of a row-partitioned SpMV over peer memory (NVLink), without a communication library
+// on the critical path.
+//
+// Every rank owns one exchange buffer that its neighbours have mapped (CUDA IPC).  A rank only ever
+// WRITES its own buffer and only READS its neighbours' buffers, with ordinary loads and stores:
+//
+//     publish   pack the values the neighbours need into this rank's buffer, then store the step number
+//               into a flag word of the same buffer (release, system scope);
+//     pull      wait until a neighbour's flag has reached the current step (acquire, system scope,
+//               bounded by a cycle budget), then copy that neighbour's packed values into this rank's
+//               own memory, where the compute kernels find them;
+//     pull_add  the same for gradients: partial sums that the neighbours computed for columns this rank
+//               owns are read from their buffers and added in ascending peer order (reproducible).
+//
+// Packed areas are double-buffered by step parity.  A rank overwrites the half of step t only after it
+// has seen every neighbour's flag reach t - 1 (its own pull of step t - 1 waited for exactly that), and a
+// neighbour publishes step t - 1 only after its pull of step t - 2 has finished: nobody can still be
+// reading the half that is being rewritten.  This needs every rank that reads from a neighbour to be read
+// by that neighbour as well, which holds for matrices whose pattern equals its transpose.
+//
+// No kernel here waits without a limit: when the budget runs out the kernel stores
+// NB200_ERR_WAIT_BUDGET into the status word and returns without copying.  Kernels of different ranks
+// wait on one another, so each rank must run on a GPU of its own.
+#include "common.cuh"
+#include <cstring>
+
+namespace nb200 {
+
+constexpr int kHaloThreads = 256;
+constexpr int kHaloDescWords = 8;   // int64 words per neighbour descriptor
+// descriptor layout (int64):
+//   [0] address of the neighbour's packed area (2 halves of [1] elements each)
+//   [1] elements per half of that area
+//   [2] first element of this rank's segment within a half
+//   [3] elements in the segment
+//   [4] first element of the destination in this rank's vector (pull only)
+//   [5] address of the neighbour's flag word for this area
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+// Loads that may not be served from a stale line of this SM's L1 (the halves are rewritten every other step)
+__device__ __forceinline__ float ld_fresh(const float* p) { return __ldcv(p); }
+__device__ __forceinline__ double ld_fresh(const double* p) { return __ldcv(p); }
+
+// Wait until *flag >= want; false if `budget` SM cycles pass first.
+__device__ __forceinline__ bool wait_for_step(const int* flag, int want, long long budget) {
+    if (ld_acquire_sys(flag) >= want) return true;
+    const long long t0 = clock64();
+    while (ld_acquire_sys(flag) < want) {
+        if (clock64() - t0 > budget) return false;
+        __nanosleep(64);
+    }
+    return true;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kHaloThreads)
+halo_publish_kernel(int64_t count, const T* __restrict__ src, const int64_t* __restrict__ idx, T* area,
+                    int* flag, int* step_word, int bump, unsigned* arrivals) {
+    // every block reads the step before any block can be the last one to arrive below
+    const int t = *step_word + (bump ? 1 : 0);
+    T* dst = area + (size_t)(t & 1) * (size_t)count;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < count; k += stride)
+        dst[k] = src[idx ? idx[k] : k];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(arrivals, 1u) == gridDim.x - 1) {
+        // last block: everything is packed and fenced; advance the step and raise the flag
+        *arrivals = 0;
+        if (bump) *step_word = t;
+        __threadfence_system();
+        st_release_sys(flag, t);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kHaloThreads)
+halo_pull_kernel(const int64_t* __restrict__ desc, T* dst_base, const int* step_word, int32_t* status, long long budget) {
+    const int64_t* d = desc + (int64_t)blockIdx.y * kHaloDescWords;
+    const int t = *step_word;
+    __shared__ int ready;
+    if (threadIdx.x == 0) {
+        ready = wait_for_step(reinterpret_cast<const int*>(d[5]), t, budget) ? 1 : 0;
+        if (!ready && status) atomicExch(status, (int)NB200_ERR_WAIT_BUDGET);
+    }
+    __syncthreads();
+    if (!ready) return;
+    const T* src = reinterpret_cast<const T*>(d[0]) + (size_t)(t & 1) * (size_t)d[1] + d[2];
+    T* dst = dst_base + d[4];
+    const int64_t count = d[3], stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < count; k += stride) dst[k] = ld_fresh(src + k);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kHaloThreads)
+halo_pull_add_kernel(int npeers, const int64_t* __restrict__ desc, int64_t ntargets,
+                     const int64_t* __restrict__ target, const int64_t* __restrict__ target_ptr,
+                     const int32_t* __restrict__ source_peer, const int64_t* __restrict__ source_elem,
+                     T* grad, const int* step_word, int32_t* status, long long budget) {
+    const int t = *step_word;
+    __shared__ int ready;
+    if (threadIdx.x == 0) {
+        int ok = 1;
+        for (int p = 0; p < npeers && ok; ++p)
+            ok = wait_for_step(reinterpret_cast<const int*>(desc[(int64_t)p * kHaloDescWords + 5]), t, budget) ? 1 : 0;
+        if (!ok && status) atomicExch(status, (int)NB200_ERR_WAIT_BUDGET);
+        ready = ok;
+    }
+    __syncthreads();
+    if (!ready) return;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < ntargets; j += stride) {
+        T acc = grad[target[j]];
+        for (int64_t c = target_ptr[j]; c < target_ptr[j + 1]; ++c) {     // neighbours in ascending order
+            const int64_t* d = desc + (int64_t)source_peer[c] * kHaloDescWords;
+            const T* half = reinterpret_cast<const T*>(d[0]) + (size_t)(t & 1) * (size_t)d[1];
+            acc = add_rn(acc, ld_fresh(half + source_elem[c]));
+        }
+        grad[target[j]] = acc;
+    }
+}
+
+static inline unsigned halo_grid(int64_t count, int cap) {
+    const int64_t want = ceil_div(count > 0 ? count : 1, (int64_t)kHaloThreads);
+    return (unsigned)(want < cap ? want : cap);
+}
+
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" int nb200_halo_publish(int64_t count, const void* src, const int64_t* idx, void* area, int32_t* flag,
+                                  int32_t* step_word, int bump_step, uint32_t* arrivals, int dtype, nb200_stream stream) {
+    if (count < 0 || !area || !flag || !step_word || !arrivals || (count > 0 && !src)) return NB200_ERR_BAD_ARG;
+    cudaStream_t st = as_stream(stream);
+    const unsigned grid = halo_grid(count, 64);
+    return NB200_DISPATCH_T(dtype,
+        (halo_publish_kernel<T><<<grid, kHaloThreads, 0, st>>>(count, (const T*)src, idx, (T*)area, flag, step_word,
+                                                               bump_step, arrivals), launch_status()));
+}
+
+extern "C" int nb200_halo_pull(int npeers, const int64_t* desc, int64_t largest_segment, void* dst,
+                               const int32_t* step_word, int32_t* status, int64_t wait_budget_cycles,
+                               int dtype, nb200_stream stream) {
+    if (npeers < 0 || largest_segment < 0 || !step_word || (npeers > 0 && (!desc || !dst))) return NB200_ERR_BAD_ARG;
+    if (npeers == 0) return NB200_OK;
+    cudaStream_t st = as_stream(stream);
+    const dim3 grid(halo_grid(largest_segment, 32), (unsigned)npeers);
+    const long long budget = wait_budget_cycles > 0 ? wait_budget_cycles : 4000000000LL;
+    return NB200_DISPATCH_T(dtype,
+        (halo_pull_kernel<T><<<grid, kHaloThreads, 0, st>>>(desc, (T*)dst, step_word, status, budget), launch_status()));
+}
+
+extern "C" int nb200_halo_pull_add(int npeers, const int64_t* desc, int64_t ntargets, const int64_t* target,
+                                   const int64_t* target_ptr, const int32_t* source_peer, const int64_t* source_elem,
+                                   void* grad, const int32_t* step_word, int32_t* status, int64_t wait_budget_cycles,
+                                   int dtype, nb200_stream stream) {
+    if (npeers < 0 || ntargets < 0 || !step_word) return NB200_ERR_BAD_ARG;
+    if (npeers == 0 || ntargets == 0) return NB200_OK;
+    if (!desc || !target || !target_ptr || !source_peer || !source_elem || !grad) return NB200_ERR_BAD_ARG;
+    cudaStream_t st = as_stream(stream);
+    const long long budget = wait_budget_cycles > 0 ? wait_budget_cycles : 4000000000LL;
+    return NB200_DISPATCH_T(dtype,
+        (halo_pull_add_kernel<T><<<halo_grid(ntargets, 128), kHaloThreads, 0, st>>>(
+             npeers, desc, ntargets, target, target_ptr, source_peer, source_elem, (T*)grad, step_word, status, budget),
+         launch_status()));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Exchange buffers.  Memory that other processes map must come from cudaMalloc directly (a block carved
+// out of a caching allocator's segment cannot be exported on its own), so these two calls are the one
+// place where the library allocates device memory -- at set-up time, never inside an operator.
+// ---------------------------------------------------------------------------------------------
+extern "C" int nb200_ipc_alloc(size_t bytes, void** ptr, void* handle64) {
+    if (!ptr || !handle64 || bytes == 0) return NB200_ERR_BAD_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is exchanged as 64 bytes");
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) return NB200_ERR_CUDA;
+    cudaIpcMemHandle_t h;
+    if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess ||
+        cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+        cudaFree(p);
+        return NB200_ERR_CUDA;
+    }
+    memcpy(handle64, &h, sizeof(h));
+    *ptr = p;
+    return NB200_OK;
+}
+
+extern "C" int nb200_ipc_free(void* ptr) {
+    if (!ptr) return NB200_OK;
+    return cudaFree(ptr) == cudaSuccess ? NB200_OK : NB200_ERR_CUDA;
+}
+
+extern "C" int nb200_ipc_open(const void* handle64, void** ptr) {
+    if (!handle64 || !ptr) return NB200_ERR_BAD_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    void* p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        return NB200_ERR_CUDA;
+    }
+    *ptr = p;
+    return NB200_OK;
+}
+
+extern "C" int nb200_ipc_close(void* ptr) {
+    if (!ptr) return NB200_OK;
+    return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? NB200_OK : NB200_ERR_CUDA;
+}

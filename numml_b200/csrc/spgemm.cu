@@ -2,11 +2,20 @@
 // and its masked backward, for CSR on sm_100a.
 //
 // Rows of C are binned by size (upper bound = number of products for the symbolic phase, exact
-// nnz for the numeric phase).  Each bin has a team size and an open-addressing hash table:
-//     bin 0:   8 lanes per row,  64-slot table in shared memory      (size <= 32)
-//     bin 1:  32 lanes per row, 512-slot table in shared memory      (size <= 256)
-//     bin 2: 256 threads per row, 8192-slot (symbolic) / 4096-slot (numeric) table in shared memory
-//     bin 3: 256 threads per row, table in a caller-provided global-memory spill area
+// nnz for the numeric phase).  Bin 0 needs no table at all:
+//     bin 0:  one warp per row, no table                             (products <= 32, entries of A <= 32)
+//             lane p owns product p in the reference's accumulation order (entries of the row of A in
+//             storage order, for each the entries of the row of B in storage order); equal columns find
+//             each other with match.any, the lowest lane of a group is its leader, a leader's position in
+//             the sorted row is the number of leaders with a smaller column, and the group's products are
+//             added in lane order -- the reference's order, so these rows come out bit-identical to its
+//             CPU loop and the same from run to run.  The next row's index chain (row of A, row pointers
+//             of B) is fetched while the current row's products are formed.
+// The other bins have a team size and an open-addressing hash table:
+//     bin 1:   8 lanes per row,  64-slot table in shared memory      (size <= 32)
+//     bin 2:  32 lanes per row, 512-slot table in shared memory      (size <= 256)
+//     bin 3: 256 threads per row, 8192-slot (symbolic) / 4096-slot (numeric) table in shared memory
+//     bin 4: 256 threads per row, table in a caller-provided global-memory spill area
 // Column keys are inserted with atomicCAS and linear probing (load factor <= 1/2); the numeric
 // phase accumulates values with shared/global atomics and then emits the row in ascending column
 // order: for 64-slot tables the occupied slots are gathered into a dense list and every entry is
@@ -25,22 +34,25 @@
 namespace nb200 {
 
 constexpr uint32_t kEmptyKey = 0xffffffffu;
-constexpr int kBins = 4;
+constexpr int kBins = 5;
+constexpr int kWarpRowMax = 32;    // products (and entries of A) a row may have to be formed by one warp
 constexpr int kHeaderWords = 16;   // int64 words at the start of the workspace
 // header layout (int64):
-//   [0..3]  rows per bin, symbolic classification (by number of products)
-//   [4]     spill slots needed by the symbolic phase (bin 3 tables)
-//   [5]     largest per-row number of products
-//   [8..11] rows per bin, numeric classification (by nnz of the output row)
-//   [12]    spill slots needed by the numeric phase
-//   [13]    nnz(C)
-//   [14]    error word (non-zero: a spill table was too small)
+//   [0..4]  rows per bin, symbolic classification (by number of products)
+//   [5]     spill slots needed by the symbolic phase (bin 4 tables)
+//   [6]     largest per-row number of products
+//   [8..12] rows per bin, numeric classification (bin 0 by products, the others by nnz of the output row)
+//   [13]    spill slots needed by the numeric phase
+//   [14]    nnz(C)
+//   [15]    error word (non-zero: a spill table was too small)
+constexpr int kHdrSymSpill = 5, kHdrMaxProducts = 6, kHdrNumBins = 8, kHdrNumSpill = 13, kHdrNnz = 14, kHdrError = 15;
 
-__host__ __device__ inline int bin_of(int64_t size, bool numeric) {
-    if (size <= 32) return 0;
-    if (size <= 256) return 1;
-    if (size <= (numeric ? 2048 : 4096)) return 2;
-    return 3;
+// hash bins 1..4 by table size needed
+__host__ __device__ inline int hash_bin_of(int64_t size, bool numeric) {
+    if (size <= 32) return 1;
+    if (size <= 256) return 2;
+    if (size <= (numeric ? 2048 : 4096)) return 3;
+    return 4;
 }
 
 __device__ __forceinline__ int64_t spill_table_size(int64_t size) {
@@ -76,27 +88,34 @@ __global__ void spgemm_products_kernel(int64_t rows, const I* __restrict__ A_ind
             const int64_t j = (int64_t)A_indices[a];
             ub += (long long)B_indptr[j + 1] - (long long)B_indptr[j];
         }
+        // a row takes the warp path only if its entries of A fit one warp too; folding their number into
+        // the size keeps one array (a larger size only means a larger table)
+        ub = max(ub, (long long)A_indptr[r + 1] - (long long)A_indptr[r]);
         if (ub > 0x7fffffffLL) ub = 0x7fffffffLL;
         size_out[r] = (int32_t)ub;
         local_max = max(local_max, ub);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) local_max = max(local_max, __shfl_xor_sync(0xffffffffu, local_max, o));
-    if ((threadIdx.x & 31) == 0 && local_max > 0) atomicMax(header + 5, (unsigned long long)local_max);
+    if ((threadIdx.x & 31) == 0 && local_max > 0) atomicMax(header + kHdrMaxProducts, (unsigned long long)local_max);
 }
 
 // Distribute rows into per-bin lists (warp-aggregated appends) and size the spill tables.
-__global__ void spgemm_classify_kernel(int64_t rows, const int32_t* __restrict__ size_in, bool numeric,
+// `products` is the array written by spgemm_products_kernel; `size_in` is that array again (symbolic
+// phase) or the exact nnz of every output row (numeric phase).
+__global__ void spgemm_classify_kernel(int64_t rows, const int32_t* __restrict__ size_in,
+                                       const int32_t* __restrict__ products, bool numeric,
                                        int32_t* __restrict__ lists, int64_t* __restrict__ spill_off,
                                        unsigned long long* __restrict__ header) {
-    const int hb = numeric ? 8 : 0;
+    const int hb = numeric ? kHdrNumBins : 0;
     const int lane = threadIdx.x & 31;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t rows_pad = (rows + 31) & ~(int64_t)31;
     for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < rows_pad; r += stride) {
         const bool ok = r < rows;
         const int32_t size = ok ? size_in[r] : 0;
-        const int bin = ok ? bin_of(size, numeric) : kBins;
+        int bin = kBins;
+        if (ok) bin = products[r] <= kWarpRowMax ? 0 : hash_bin_of(size, numeric);
         const uint32_t peers = __match_any_sync(0xffffffffu, bin);
         if (ok) {
             const int leader = __ffs(peers) - 1;
@@ -105,8 +124,105 @@ __global__ void spgemm_classify_kernel(int64_t rows, const int32_t* __restrict__
             base = __shfl_sync(peers, base, leader);
             const int64_t pos = (int64_t)base + __popc(peers & ((1u << lane) - 1u));
             lists[(int64_t)bin * rows + pos] = (int32_t)r;
-            if (bin == 3) spill_off[pos] = (int64_t)atomicAdd(header + hb + 4, (unsigned long long)spill_table_size(size));
+            if (bin == 4) spill_off[pos] = (int64_t)atomicAdd(header + hb + kHdrSymSpill, (unsigned long long)spill_table_size(size));
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Bin 0: one warp per row, no table.
+// ---------------------------------------------------------------------------------------------
+template <typename T, typename I>
+struct WarpRow {          // what the lanes hold about a row before its products are formed
+    int64_t row;
+    int64_t b_begin;      // lane e < na: first position of the row of B that entry e of the row of A selects
+    int len;              // lane e < na: length of that row of B
+    int na;               // entries of the row of A
+    T a_val;              // lane e < na: value of entry e (numeric phase)
+};
+
+template <typename T, typename I, bool NUMERIC>
+__device__ __forceinline__ WarpRow<T, I> warp_row_fetch(int64_t idx, int64_t count, int lane, const int32_t* __restrict__ list,
+                                                        const T* __restrict__ A_data, const I* __restrict__ A_indices,
+                                                        const I* __restrict__ A_indptr, const I* __restrict__ B_indptr) {
+    WarpRow<T, I> w{0, 0, 0, 0, (T)0};
+    if (idx < count) {
+        w.row = (int64_t)list[idx];
+        const int64_t a0 = (int64_t)A_indptr[w.row];
+        w.na = (int)((int64_t)A_indptr[w.row + 1] - a0);
+        if (lane < w.na) {
+            const int64_t j = (int64_t)A_indices[a0 + lane];
+            w.b_begin = (int64_t)B_indptr[j];
+            w.len = (int)((int64_t)B_indptr[j + 1] - w.b_begin);
+            if (NUMERIC) w.a_val = A_data[a0 + lane];
+        }
+    }
+    return w;
+}
+
+template <typename T, typename I, bool NUMERIC>
+__global__ void __launch_bounds__(256)
+spgemm_warp_rows_kernel(const int32_t* __restrict__ list, const unsigned long long* __restrict__ count_ptr,
+                        const T* __restrict__ A_data, const I* __restrict__ A_indices, const I* __restrict__ A_indptr,
+                        const T* __restrict__ B_data, const I* __restrict__ B_indices, const I* __restrict__ B_indptr,
+                        int32_t* __restrict__ row_nnz, const int64_t* __restrict__ C_indptr,
+                        int64_t* __restrict__ C_indices, T* __restrict__ C_data) {
+    constexpr unsigned kAll = 0xffffffffu;
+    const int lane = threadIdx.x & 31;
+    const int64_t count = (int64_t)*count_ptr;
+    const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    int64_t idx = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    WarpRow<T, I> cur = warp_row_fetch<T, I, NUMERIC>(idx, count, lane, list, A_data, A_indices, A_indptr, B_indptr);
+    for (; idx < count; idx += nwarps) {
+        // the next row's index chain is in flight while this row's products are formed
+        const WarpRow<T, I> nxt = warp_row_fetch<T, I, NUMERIC>(idx + nwarps, count, lane, list, A_data, A_indices, A_indptr, B_indptr);
+        int64_t c_begin = 0;
+        if (NUMERIC) c_begin = C_indptr[cur.row];
+        // products of entry e occupy lanes [incl_e - len_e, incl_e)
+        int incl = cur.len;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(kAll, incl, o);
+            if (lane >= o) incl += t;
+        }
+        const int np = __shfl_sync(kAll, incl, 31);
+        const bool valid = lane < np;
+        int e = 0;                                     // the entry of A that product `lane` belongs to
+        for (int q = 0; q < cur.na; ++q) e += (__shfl_sync(kAll, incl, q) <= lane);
+        if (!valid) e = 0;
+        const int first = __shfl_sync(kAll, incl - cur.len, e);
+        const int64_t b0 = __shfl_sync(kAll, cur.b_begin, e);
+        T a_e = (T)0;
+        if (NUMERIC) a_e = __shfl_sync(kAll, cur.a_val, e);
+        uint32_t c = kEmptyKey;                        // lanes without a product share a column no row has
+        T v = (T)0;
+        if (valid) {
+            const int64_t b = b0 + (lane - first);
+            c = (uint32_t)B_indices[b];
+            if (NUMERIC) v = mul_rn(a_e, B_data[b]);
+        }
+        const unsigned group = __match_any_sync(kAll, c);
+        const bool leader = valid && lane == __ffs(group) - 1;
+        const unsigned leaders = __ballot_sync(kAll, leader);
+        if (!NUMERIC) {
+            if (lane == 0) row_nnz[cur.row] = __popc(leaders);
+        } else {
+            int rank = 0;                              // position in the sorted row: leaders with a smaller column
+            for (unsigned rem = leaders; rem; rem &= rem - 1) rank += __shfl_sync(kAll, c, __ffs(rem) - 1) < c;
+            // the group's products in lane order = the reference's order of additions
+            const int longest = __reduce_max_sync(kAll, valid ? __popc(group) : 0);
+            T sum = (T)0;
+            unsigned rem = group;
+            for (int it = 0; it < longest; ++it) {
+                const T t = __shfl_sync(kAll, v, rem ? __ffs(rem) - 1 : lane);
+                if (rem) { sum = add_rn(sum, t); rem &= rem - 1; }
+            }
+            if (leader) {
+                C_indices[c_begin + rank] = (int64_t)c;
+                C_data[c_begin + rank] = sum;
+            }
+        }
+        cur = nxt;
     }
 }
 
@@ -186,7 +302,7 @@ spgemm_symbolic_kernel(const int32_t* __restrict__ list, const unsigned long lon
             const int64_t off = spill_off[idx];
             usable = off + table <= spill_slots;
             keys = spill + off;
-            if (!usable && t == 0) atomicExch(header + 14, 1ull);
+            if (!usable && t == 0) atomicExch(header + kHdrError, 1ull);
         }
         int shift = 32;
         for (int64_t s = table; s > 1; s >>= 1) --shift;
@@ -247,7 +363,7 @@ spgemm_numeric_kernel(const int32_t* __restrict__ list, const unsigned long long
             usable = off + table <= spill_slots;
             keys = spill_keys + off;
             vals = spill_vals + off;
-            if (!usable && t == 0) atomicExch(header + 14, 1ull);
+            if (!usable && t == 0) atomicExch(header + kHdrError, 1ull);
         }
         int shift = 32;
         for (int64_t s = table; s > 1; s >>= 1) --shift;
@@ -426,7 +542,7 @@ int spgemm_plan(int64_t A_rows, const I* A_indices, const I* A_indptr, const I* 
     if (cudaMemsetAsync(w.header, 0, kHeaderWords * sizeof(int64_t), st) != cudaSuccess) return NB200_ERR_CUDA;
     if (A_rows == 0) return NB200_OK;
     spgemm_products_kernel<I><<<flat_grid(A_rows), 256, 0, st>>>(A_rows, A_indices, A_indptr, B_indptr, w.size, w.header);
-    spgemm_classify_kernel<<<flat_grid(A_rows), 256, 0, st>>>(A_rows, w.size, false, w.lists, w.spill_off, w.header);
+    spgemm_classify_kernel<<<flat_grid(A_rows), 256, 0, st>>>(A_rows, w.size, w.size, false, w.lists, w.spill_off, w.header);
     return launch_status();
 }
 
@@ -438,23 +554,25 @@ int spgemm_symbolic(int64_t A_rows, const I* A_indices, const I* A_indptr, const
     if (!w.ok) return NB200_ERR_WORKSPACE;
     if (A_rows > 0) {
         const unsigned g = persistent_grid();
+        spgemm_warp_rows_kernel<double, I, false><<<g, 256, 0, st>>>(
+            w.lists, w.header + 0, nullptr, A_indices, A_indptr, nullptr, B_indices, B_indptr, w.row_nnz, nullptr, nullptr, nullptr);
 #define NB200_SYM(TEAM, SUB, TLOG, SPILL, BIN)                                                              \
         spgemm_symbolic_kernel<I, TEAM, SUB, TLOG, SPILL><<<g, 256, 0, st>>>(                                 \
             w.lists + (int64_t)(BIN) * A_rows, w.header + (BIN), A_indices, A_indptr, B_indices, B_indptr,  \
             w.size, w.spill_off, spill, spill_slots, w.header, w.row_nnz)
-        NB200_SYM(8, 1, 6, false, 0);
-        NB200_SYM(32, 4, 9, false, 1);
-        NB200_SYM(256, 32, 13, false, 2);
-        NB200_SYM(256, 32, 0, true, 3);
+        NB200_SYM(8, 1, 6, false, 1);
+        NB200_SYM(32, 4, 9, false, 2);
+        NB200_SYM(256, 32, 13, false, 3);
+        NB200_SYM(256, 32, 0, true, 4);
 #undef NB200_SYM
     }
     int rc = exclusive_scan_i32_to_i64(A_rows, w.row_nnz, C_indptr, w.scan, w.scan_bytes, st);
     if (rc != NB200_OK) return rc;
     if (A_rows > 0) {
         // numeric classification by exact row size; nnz(C) goes to header[13]
-        spgemm_classify_kernel<<<flat_grid(A_rows), 256, 0, st>>>(A_rows, w.row_nnz, true, w.lists, w.spill_off, w.header);
+        spgemm_classify_kernel<<<flat_grid(A_rows), 256, 0, st>>>(A_rows, w.row_nnz, w.size, true, w.lists, w.spill_off, w.header);
     }
-    if (cudaMemcpyAsync(w.header + 13, C_indptr + A_rows, sizeof(int64_t), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+    if (cudaMemcpyAsync(w.header + kHdrNnz, C_indptr + A_rows, sizeof(int64_t), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
         return NB200_ERR_CUDA;
     return launch_status();
 }
@@ -471,14 +589,16 @@ int spgemm_numeric(int64_t A_rows, const T* A_data, const I* A_indices, const I*
     T* spill_vals = static_cast<T*>(spill);
     uint32_t* spill_keys = reinterpret_cast<uint32_t*>(spill_vals + (spill_slots > 0 ? spill_slots : 0));
     const unsigned g = persistent_grid();
+    spgemm_warp_rows_kernel<T, I, true><<<g, 256, 0, st>>>(
+        w.lists, w.header + kHdrNumBins, A_data, A_indices, A_indptr, B_data, B_indices, B_indptr, nullptr, C_indptr, C_indices, C_data);
 #define NB200_NUM(TEAM, SUB, TLOG, SPILL, BIN)                                                                   \
     spgemm_numeric_kernel<T, I, TEAM, SUB, TLOG, SPILL><<<g, 256, 0, st>>>(                                       \
-        w.lists + (int64_t)(BIN) * A_rows, w.header + 8 + (BIN), A_data, A_indices, A_indptr, B_data, B_indices, \
+        w.lists + (int64_t)(BIN) * A_rows, w.header + kHdrNumBins + (BIN), A_data, A_indices, A_indptr, B_data, B_indices, \
         B_indptr, w.row_nnz, w.spill_off, spill_keys, spill_vals, spill_slots, w.header, C_indptr, C_indices, C_data)
-    NB200_NUM(8, 1, 6, false, 0);
-    NB200_NUM(32, 4, 9, false, 1);
-    NB200_NUM(256, 32, 12, false, 2);
-    NB200_NUM(256, 32, 0, true, 3);
+    NB200_NUM(8, 1, 6, false, 1);
+    NB200_NUM(32, 4, 9, false, 2);
+    NB200_NUM(256, 32, 12, false, 3);
+    NB200_NUM(256, 32, 0, true, 4);
 #undef NB200_NUM
     return launch_status();
 }

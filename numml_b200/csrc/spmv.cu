@@ -15,6 +15,7 @@
 // structure whose values are gathered through a permutation (atomic-free, deterministic).
 #include "common.cuh"
 #include "spmv_pipe.cuh"
+#include <type_traits>
 
 namespace nb200 {
 
@@ -283,11 +284,11 @@ template <typename T, typename I>
 int spmv_backward_launch(int64_t rows, int64_t cols, int64_t nnz, const T* data, const I* indices,
                          const I* indptr, const T* x, const T* g, const I* t_indptr,
                          const I* t_indices, const I* t_perm, T* grad_A, T* grad_x, int block_rows, int t_block_rows,
-                         bool pattern_symmetric, int32_t* status, cudaStream_t st) {
+                         int symmetry, int32_t* status, cudaStream_t st) {
     const bool atomic = (t_indptr == nullptr);
-    if (!atomic && pattern_symmetric && block_rows > 0 && rows == cols && nnz > 0)
+    if (!atomic && (symmetry & NB200_SYMMETRIC_PATTERN) && block_rows > 0 && rows == cols && nnz > 0)
         return spmv_pipe_backward_sym<T, I>(0, rows, nnz, block_rows, data, indices, indptr, t_perm, x, g, grad_A, grad_x,
-                                            status, st);
+                                            (symmetry & NB200_SYMMETRIC_VALUES) != 0, status, st);
     if (atomic && cols > 0) {
         if (cudaMemsetAsync(grad_x, 0, sizeof(T) * (size_t)cols, st) != cudaSuccess) return NB200_ERR_CUDA;
     }
@@ -363,7 +364,7 @@ extern "C" int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
         (spmv_backward_launch<T, I>(rows, cols, nnz, (const T*)data, (const I*)indices, (const I*)indptr,
                                     (const T*)x, (const T*)g, (const I*)t_indptr, (const I*)t_indices,
                                     (const I*)t_perm, (T*)grad_A, (T*)grad_x, block_rows, t_block_rows,
-                                    pattern_symmetric != 0, status, as_stream(stream))));
+                                    pattern_symmetric, status, as_stream(stream))));
 }
 
 
@@ -373,19 +374,47 @@ extern "C" int nb200_spgemv_backward(int64_t rows, int64_t cols, int64_t nnz,
 extern "C" int nb200_spgemv_backward_symmetric_rows(int64_t n, int64_t nnz, int64_t row_begin, int64_t row_end,
                                                     const void* data, const void* indices, const void* indptr,
                                                     const void* t_perm, const void* x, const void* g,
-                                                    void* grad_A, void* grad_x, int block_rows, int32_t* status,
-                                                    int dtype, int itype, nb200_stream stream) {
+                                                    void* grad_A, void* grad_x, int values_symmetric, int block_rows,
+                                                    int32_t* status, int dtype, int itype, nb200_stream stream) {
     if (n < 0 || nnz < 0 || row_begin < 0 || row_end < row_begin || row_end > n) return NB200_ERR_BAD_ARG;
     if (block_rows < 1 || block_rows > 256) return NB200_ERR_BAD_ARG;
     if (row_end == row_begin || nnz == 0) return NB200_OK;
     if (!data || !indices || !indptr || !t_perm || !x || !g || !grad_A || !grad_x) return NB200_ERR_BAD_ARG;
     // bulk copies of the index streams and two-entry vector stores of grad_A
-    if (!aligned16(indices) || !aligned16(t_perm) || !aligned16(grad_A)) return NB200_ERR_ALIGN;
+    if (!aligned16(indices) || !aligned16(t_perm) || !aligned16(grad_A) || (values_symmetric && !aligned16(data))) return NB200_ERR_ALIGN;
     if (itype == NB200_I32 && nnz > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
     return NB200_DISPATCH(dtype, itype,
         (spmv_pipe_backward_sym<T, I>(row_begin, row_end, nnz, block_rows, (const T*)data, (const I*)indices,
                                       (const I*)indptr, (const I*)t_perm, (const T*)x, (const T*)g, (T*)grad_A,
-                                      (T*)grad_x, status, as_stream(stream))));
+                                      (T*)grad_x, values_symmetric != 0, status, as_stream(stream))));
+}
+
+// Does A equal its transpose in value?  With t_perm[k] = position in A of the mirror image of entry k
+// (the permutation of the transposed structure of a pattern that equals its transpose), that is
+// data[t_perm[k]] == data[k] for every k, compared as bit patterns.  The device word `mismatch` is
+// OR-ed with 1 when some entry differs; the caller zeroes it first.
+namespace nb200 {
+template <typename T, typename I>
+__global__ void values_symmetric_kernel(int64_t nnz, const T* __restrict__ data, const I* __restrict__ t_perm,
+                                        int32_t* __restrict__ mismatch) {
+    using Bits = typename std::conditional<sizeof(T) == 8, unsigned long long, unsigned int>::type;
+    const Bits* bits = reinterpret_cast<const Bits*>(data);
+    bool differs = false;
+    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < nnz; k += (int64_t)gridDim.x * blockDim.x)
+        differs |= bits[k] != __ldg(bits + t_perm[k]);
+    if (__any_sync(0xffffffffu, differs) && (threadIdx.x & 31) == 0) atomicOr(mismatch, 1);
+}
+}  // namespace nb200
+
+extern "C" int nb200_csr_values_symmetric(int64_t nnz, const void* data, const void* t_perm, int32_t* mismatch,
+                                          int dtype, int itype, nb200_stream stream) {
+    if (nnz < 0 || !mismatch || (nnz > 0 && (!data || !t_perm))) return NB200_ERR_BAD_ARG;
+    if (nnz == 0) return NB200_OK;
+    const int64_t want = ceil_div(nnz, (int64_t)1024);
+    const unsigned grid = (unsigned)(want > (int64_t)kSMs * 16 ? (int64_t)kSMs * 16 : want);
+    return NB200_DISPATCH(dtype, itype,
+        (values_symmetric_kernel<T, I><<<grid, 256, 0, as_stream(stream)>>>(nnz, (const T*)data, (const I*)t_perm, mismatch),
+         launch_status()));
 }
 
 // grad_A alone (the masked outer product g x^T on the pattern), for callers that schedule the

@@ -18,11 +18,16 @@
 //   kGradA         stage = column indices                      grad_A[k] = g[row(k)] x[col[k]]
 //   kBackwardSym   stage = column indices + permutation        both gradients in one pass, for patterns that
 //                                                              equal their transpose (stencils, undirected graphs)
+//   kBackwardSymVal stage = values + column indices            the same pass for a matrix whose VALUES equal their
+//                                                              transpose too (A[i,c] == A[c,i] bit for bit, which the
+//                                                              caller has checked): the transposed value of an entry is
+//                                                              the entry's own value, so no permutation is read and
+//                                                              no value is gathered
 // The fused backward gathers three operands per entry (x, g and the transposed value).  Its row threads
 // fetch them with per-thread asynchronous copies (cp.async) into shared-memory slots instead of into
 // registers, eight entries at a time, so that a short row has all of its gathers in flight at once.
 //
-// Every wait on an mbarrier is a bounded try_wait loop; if the bound is hit the CTA records
+// Every wait on an mbarrier is a try_wait loop bounded by a cycle budget; if it runs out the CTA records
 // NB200_ERR_WAIT_BUDGET in the status word (when one is given) and leaves its block loop.
 #include "spmv_pipe.cuh"
 #include <atomic>
@@ -30,12 +35,13 @@
 namespace nb200 {
 
 constexpr int kPipeTile = kSpmvPipeTile;   // nonzeros per stage
-constexpr int kPipeConsumers = 256;   // consumer threads (8 warps); one more warp produces
+constexpr int kPipeConsumers = kSpmvPipeRows;   // consumer threads (8 warps); one more warp produces
 constexpr int kPipeThreads = kPipeConsumers + 32;
-constexpr unsigned kPipeSpinLimit = 1u << 24;
+constexpr long long kPipeWaitCycles = 4000000000LL;   // wait budget in SM cycles (about two seconds)
 constexpr int kMaxDevices = 64;        // devices one process can address
 
-enum PipeMode { kForward = 0, kForwardPerm = 1, kGradA = 2, kBackwardSym = 3 };
+enum PipeMode { kForward = 0, kForwardPerm = 1, kGradA = 2, kBackwardSym = 3, kBackwardSymVal = 4 };
+__host__ __device__ constexpr bool is_backward_sym(int mode) { return mode == kBackwardSym || mode == kBackwardSymVal; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -49,16 +55,20 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, unsigned by
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}"
                  :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait for the phase with the given parity; false if the bound was hit.
+// Bounded wait for the phase with the given parity; false if kPipeWaitCycles SM cycles passed first.
+__device__ __forceinline__ bool mbar_try(uint32_t addr, unsigned parity) {
+    unsigned done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    return done != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
     const uint32_t addr = smem_u32(bar);
-    for (unsigned spins = 0; spins < kPipeSpinLimit; ++spins) {
-        unsigned done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
+    if (mbar_try(addr, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try(addr, parity))
+        if (clock64() - t0 > kPipeWaitCycles) return false;
+    return true;
 }
 // Bulk copy global -> shared, completion signalled on `bar`.  16-byte aligned, size % 16 == 0.
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
@@ -91,16 +101,17 @@ template <typename T, typename I, int MODE, int S, bool DIRECT = false, int GATH
 struct PipeSmem {
     static constexpr bool has_a = MODE != kGradA;
     static constexpr bool a_is_perm = MODE == kForwardPerm || MODE == kBackwardSym;
-    static constexpr bool has_p = (MODE == kGradA || MODE == kBackwardSym) && !DIRECT;
+    static constexpr bool has_p = (MODE == kGradA || is_backward_sym(MODE)) && !DIRECT;
     static constexpr size_t a_bytes = has_a ? (a_is_perm ? sizeof(I) : sizeof(T)) * kPipeTile : 0;  // values | perm
     static constexpr size_t b_bytes = sizeof(I) * kPipeTile;                                           // indices
     static constexpr size_t p_bytes = has_p ? sizeof(T) * kPipeTile : 0;                               // grad_A staging
     static constexpr size_t stage_bytes = a_bytes + b_bytes + p_bytes;
     static constexpr size_t header_bytes = 128;
-    // three planes (g_c, transposed value, x_c) of one slot per (entry position, consumer thread)
-    static constexpr size_t gather_bytes = 3 * sizeof(T) * GATHER * kPipeConsumers;
+    // planes (g_c, transposed value unless it is staged, x_c) of one slot per (entry position, consumer thread)
+    static constexpr int gather_planes = MODE == kBackwardSymVal ? 2 : 3;
+    static constexpr size_t gather_bytes = gather_planes * sizeof(T) * GATHER * kPipeConsumers;
     static constexpr size_t total = header_bytes + stage_bytes * S + gather_bytes;
-    static_assert(GATHER == 0 || (MODE == kBackwardSym && DIRECT), "GATHER is a variant of the fused backward");
+    static_assert(GATHER == 0 || (is_backward_sym(MODE) && DIRECT), "GATHER is a variant of the fused backward");
 };
 
 template <typename T> struct Pair;
@@ -155,6 +166,9 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kPipeStages;
+    // iteration (plus one) in which a consumer warp gave up waiting; read after the consumers' barrier
+    volatile int* const gave_up = reinterpret_cast<volatile int*>(smem + L::header_bytes - sizeof(int));
+    static_assert(2 * S * sizeof(uint64_t) + sizeof(int) <= L::header_bytes, "barriers and the abort word share the header");
     auto stage_ptr = [&](int s) { return smem + L::header_bytes + (size_t)s * L::stage_bytes; };
     // per stage: [A: values or perm (absent for kGradA)] [B: indices] [P: grad_A staging (kGradA only)]
     auto stage_A = [&](int s) { return stage_ptr(s); };
@@ -164,6 +178,7 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
     const int tid = threadIdx.x;
     if (tid == 0) {
         for (int s = 0; s < kPipeStages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, kPipeConsumers / 32); }
+        *gave_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -195,7 +210,7 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
             if (count == 0) { mbar_arrive(full + s); continue; }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             const unsigned bytes_b = (unsigned)(count * sizeof(I));
-            if (MODE == kForward) {
+            if (MODE == kForward || MODE == kBackwardSymVal) {
                 const unsigned bytes_a = (unsigned)(count * sizeof(T));
                 mbar_arrive_expect_tx(full + s, bytes_a + bytes_b);
                 bulk_load(stage_A(s), a.data + base, bytes_a, full + s);
@@ -227,7 +242,7 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
             if (tid < a.block_rows && r < r1) {
                 f.lo = (int)min((int64_t)a.indptr[r] - f.begin, (int64_t)0x3fffffff);
                 f.hi = (int)min((int64_t)a.indptr[r + 1] - f.begin, (int64_t)0x3fffffff);
-                if (MODE == kGradA || MODE == kBackwardSym) f.g = a.rowvec[r];
+                if (MODE == kGradA || is_backward_sym(MODE)) f.g = a.rowvec[r];
             }
         }
         return f;
@@ -248,9 +263,19 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
         const bool owns_row = tid < a.block_rows && r0 + tid < r1;
         const int staged_cnt = (int)max(bulk_stop - base, (int64_t)0);   // stage offsets below this hold data
 
-        if (!mbar_wait(full + s, ph)) {
-            if (a.status && tid == 0) atomicExch(a.status, (int)NB200_ERR_WAIT_BUDGET);
-            return;
+        // The decision to give up is taken per warp (all lanes or none).  Kernels without a barrier among
+        // the consumers let such a warp leave: the producer then runs out of its own budget on the stage
+        // the warp never releases, and so do the other warps on their next wait.  Kernels that stage
+        // grad_A meet at a barrier once per block; there the warp skips its work, still arrives, and
+        // everybody leaves together after the barrier.
+        constexpr bool kConsumersMeet = (MODE == kGradA || is_backward_sym(MODE)) && !DIRECT;
+        const bool stage_ready = __all_sync(0xffffffffu, mbar_wait(full + s, ph));
+        if (!stage_ready) {
+            if ((tid & 31) == 0) {
+                if (a.status) atomicExch(a.status, (int)NB200_ERR_WAIT_BUDGET);
+                *gave_up = (int)(it & 0x3fffffff) + 1;
+            }
+            if (!kConsumersMeet) return;
         }
         const I* sidx = reinterpret_cast<const I*>(stage_B(s));
         const T* sval = reinterpret_cast<const T*>(stage_A(s));     // kForward
@@ -259,13 +284,14 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
         T* const outp = a.out + base;                                // entry with stage offset o is out[base + o]
 
         // ---- one thread per row: entries from the stage, x through L1/L2, storage order ----
-        if (MODE == kBackwardSym && GATHER > 0) {
-            if (owns_row) {
+        if (is_backward_sym(MODE) && GATHER > 0) {
+            if (owns_row && stage_ready) {
                 using T2 = typename Pair<T>::type;
+                constexpr bool kStagedValues = MODE == kBackwardSymVal;
                 constexpr int kPlane = GATHER * kPipeConsumers;
                 T* const sg = reinterpret_cast<T*>(smem + L::header_bytes + (size_t)kPipeStages * L::stage_bytes) + tid;
-                T* const sd = sg + kPlane;
-                T* const sx = sd + kPlane;
+                T* const sx = sg + kPlane;
+                T* const sd = sx + kPlane;                               // unused when the values are staged
                 const int o_lo = cur.lo + shift, o_hi = cur.hi + shift;
                 const int o_staged = min(o_hi, staged_cnt);              // below o_hi only at the ragged end of the arrays
                 const T gi = cur.g;
@@ -274,10 +300,10 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
                     const int n = min(GATHER, o_staged - o0);
                     // (1) every gather of the chunk at once: x_c, g_c and A^T[i, c] = data[perm[k]]
                     for (int e = 0; e < n; ++e) {
-                        const I c = sidx[o0 + e], q = sperm[o0 + e];
+                        const I c = sidx[o0 + e];
                         async_copy_elem(sx + e * kPipeConsumers, a.vec + c);
                         async_copy_elem(sg + e * kPipeConsumers, a.rowvec + c);
-                        async_copy_elem(sd + e * kPipeConsumers, a.data + q);
+                        if (!kStagedValues) async_copy_elem(sd + e * kPipeConsumers, a.data + sperm[o0 + e]);
                     }
                     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
                     // (2) grad_A[k] = g_i x_c, two entries per vector store where the address allows
@@ -293,16 +319,17 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
                     // (3) grad_x[i] += A^T[i, c] g_c in storage order
 #pragma unroll
                     for (int j = 0; j < GATHER; ++j)
-                        if (j < n) acc = add_rn(acc, mul_rn(sg[j * kPipeConsumers], sd[j * kPipeConsumers]));
+                        if (j < n) acc = add_rn(acc, mul_rn(sg[j * kPipeConsumers], kStagedValues ? sval[o0 + j] : sd[j * kPipeConsumers]));
                 }
                 for (int o = max(o_staged, o_lo); o < o_hi; ++o) {       // entries that were not staged: plain loads
                     const I c = a.indices[base + o];
                     outp[o] = mul_rn(gi, ldg(a.vec + c));
-                    acc = add_rn(acc, mul_rn(ldg(a.rowvec + c), ldg(a.data + a.perm[base + o])));
+                    const T tv = kStagedValues ? a.data[base + o] : ldg(a.data + a.perm[base + o]);
+                    acc = add_rn(acc, mul_rn(ldg(a.rowvec + c), tv));
                 }
                 a.out2[r0 + tid] = acc;
             }
-        } else if (owns_row) {
+        } else if (owns_row && stage_ready) {
             T acc = 0;
             const int o_lo = cur.lo + shift, o_hi = cur.hi + shift;
             const bool all_staged = o_hi <= staged_cnt;              // false only at the ragged end of the arrays
@@ -317,19 +344,19 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
                         const int o = o0 + j;
                         if (all_staged || o < staged_cnt) {
                             c[j] = sidx[o];
-                            if (MODE == kForward) v[j] = sval[o];
+                            if (MODE == kForward || MODE == kBackwardSymVal) v[j] = sval[o];
                             if (MODE == kForwardPerm || MODE == kBackwardSym) v[j] = ldg(a.data + sperm[o]);
                         } else {
                             const int64_t k = base + o;
                             c[j] = a.indices[k];
-                            if (MODE == kForward) v[j] = a.data[k];
+                            if (MODE == kForward || MODE == kBackwardSymVal) v[j] = a.data[k];
                             if (MODE == kForwardPerm || MODE == kBackwardSym) v[j] = ldg(a.data + a.perm[k]);
                         }
                     }
                 }
 #pragma unroll
                 for (int j = 0; j < CH; ++j) xv[j] = (j < n) ? ldg(a.vec + c[j]) : (T)0;
-                if (MODE == kBackwardSym) {
+                if (is_backward_sym(MODE)) {
                     // the pattern equals its transpose: row i of A^T has the same columns, so one pass
                     // gives grad_A[k] = g_i x_c and grad_x[i] = sum_k A^T[i,c] g_c
                     T gv[CH];
@@ -360,11 +387,12 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
                 }
             }
             if (MODE == kForward || MODE == kForwardPerm) a.out[r0 + tid] = acc;
-            if (MODE == kBackwardSym) a.out2[r0 + tid] = acc;
+            if (is_backward_sym(MODE)) a.out2[r0 + tid] = acc;
         }
-        if ((MODE == kGradA || MODE == kBackwardSym) && !DIRECT) {
+        if ((MODE == kGradA || is_backward_sym(MODE)) && !DIRECT) {
             // ---- coalesced 128-bit stores of the block's grad_A entries ----
             consumer_sync();
+            if (*gave_up == (int)(it & 0x3fffffff) + 1) return;
             const int64_t lim = min(end, base + kPipeTile);
 #pragma unroll
             for (int u = 0; u < kPipeTile / (kPipeConsumers * 4); ++u) {
@@ -429,12 +457,33 @@ int spmv_pipe_grad_A(int64_t rows, int64_t nnz, int block_rows, const I* indices
     return spmv_pipe_launch<T, I, kGradA, 2, 4, 4>(a, st);
 }
 
+#ifndef NB200_SYMVAL_VARIANT
+#define NB200_SYMVAL_VARIANT 0
+#endif
+
 template <typename T, typename I>
 int spmv_pipe_backward_sym(int64_t row_begin, int64_t row_end, int64_t nnz, int block_rows, const T* data,
                            const I* indices, const I* indptr, const I* perm, const T* x, const T* g, T* grad_A,
-                           T* grad_x, int32_t* status, cudaStream_t st) {
+                           T* grad_x, bool values_symmetric, int32_t* status, cudaStream_t st) {
     if (row_end <= row_begin) return NB200_OK;
     PipeArgs<T, I> a{row_begin, row_end, nnz, ceil_div(row_end - row_begin, (int64_t)block_rows), block_rows, data, indices, indptr, perm, x, g, grad_A, grad_x, status};
+    if (values_symmetric) {
+        // values and indices staged by bulk copies, x_c and g_c gathered: the traffic is exactly the
+        // credited bytes of the backward (no permutation, no value gather)
+#if NB200_SYMVAL_VARIANT == 0
+        return spmv_pipe_launch<T, I, kBackwardSymVal, 2, 4, 4, true, 0>(a, st);
+#elif NB200_SYMVAL_VARIANT == 1
+        return spmv_pipe_launch<T, I, kBackwardSymVal, 2, 2, 4, true, 0>(a, st);
+#elif NB200_SYMVAL_VARIANT == 2
+        return spmv_pipe_launch<T, I, kBackwardSymVal, 2, 2, 2, true, 8>(a, st);
+#elif NB200_SYMVAL_VARIANT == 3
+        return spmv_pipe_launch<T, I, kBackwardSymVal, 2, 2, 3, true, 4>(a, st);
+#elif NB200_SYMVAL_VARIANT == 4
+        return spmv_pipe_launch<T, I, kBackwardSymVal, 2, 8, 3, true, 0>(a, st);
+#else
+        return spmv_pipe_launch<T, I, kBackwardSymVal, 3, 4, 3, true, 0>(a, st);
+#endif
+    }
     // Measured on the 128^3 Poisson matrix (us).  Gathers into registers, grad_A written straight from the
     // row threads: 2 stages / 2 entries per round / 4 CTAs per SM 94.5; 2/4/4 98; 4/4/3 104; 3/8/3 112; 5+ CTAs
     // per SM spill; grad_A staged in shared memory for coalesced stores 107.  Asynchronous gathers into
@@ -451,7 +500,7 @@ int spmv_pipe_backward_sym(int64_t row_begin, int64_t row_end, int64_t nnz, int 
     template int spmv_pipe_grad_A<T, I>(int64_t, int64_t, int, const I*, const I*, const T*, const T*, T*, int32_t*,  \
                                         cudaStream_t);                                                               \
     template int spmv_pipe_backward_sym<T, I>(int64_t, int64_t, int64_t, int, const T*, const I*, const I*, const I*, \
-                                              const T*, const T*, T*, T*, int32_t*, cudaStream_t);
+                                              const T*, const T*, T*, T*, bool, int32_t*, cudaStream_t);
 NB200_INSTANTIATE_PIPE(float, int32_t)
 NB200_INSTANTIATE_PIPE(float, int64_t)
 NB200_INSTANTIATE_PIPE(double, int32_t)

@@ -21,6 +21,9 @@ spmv_backward_mode = "transpose"
 # regular enough (every block of 256 or 128 rows fits one pipeline stage) and the register-staged
 # streaming kernels otherwise; "stream" forces the latter.  Results are identical.
 spmv_kernel = "auto"
+# Whether the one-pass backward may use the value-symmetric variant (the matrix equals its transpose
+# in value too, established by a cached device-side test; see PatternPlan.values_symmetric).
+spmv_value_symmetry = True
 
 
 def _dtype_code(t):
@@ -133,6 +136,8 @@ def spgemv_backward(grad_z, A_rows, A_cols, A_data, A_col_ind, A_rowptr, x):
         block_rows = plan.spmv_block_rows() if auto else 0
         t_block_rows = plan.spmv_block_rows(transposed=True) if (auto and t_indptr is not None) else 0
         symmetric = int(auto and t_indptr is not None and block_rows > 0 and plan.pattern_symmetric())
+        if symmetric and spmv_value_symmetry and plan.values_symmetric(A_data):
+            symmetric |= 2          # NB200_SYMMETRIC_VALUES
         grad_A = torch.empty_like(A_data)
         grad_x = torch.empty(A_cols, dtype=A_data.dtype, device=dev)
         _cabi.call("nb200_spgemv_backward", A_rows, A_cols, plan.nnz, _ptr(A_data), _ptr(idx), _ptr(ptr),
@@ -232,6 +237,10 @@ def _common_width(plan_a, plan_b):
     return plan_a.indices, plan_a.indptr, plan_b.indices, plan_b.indptr, _cabi.I64
 
 
+# positions in the 16-word header of an SpGEMM workspace (see nb200_spgemm_plan in the C header)
+_HDR_SYM_SPILL, _HDR_NUM_SPILL, _HDR_NNZ, _HDR_ERROR = 5, 13, 14, 15
+
+
 def _header(work):
     """The 16-word int64 header at the start of an SpGEMM workspace (device-to-host copy, syncs)."""
     return work[:128].view(torch.int64).cpu()
@@ -249,17 +258,26 @@ def spgemm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B_rows, B_cols, 
     with _on(dev):
         wbytes = _cabi.lib().nb200_spgemm_workspace_bytes(A_rows)
         work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
-        _cabi.call("nb200_spgemm_plan", A_rows, A_cols, plan_a.nnz, _ptr(ai), _ptr(ap), _ptr(bp), itype,
-                   _ptr(work), wbytes, _stream())
-        slots = int(_header(work)[4])
-        spill = torch.empty(slots * 4, dtype=torch.uint8, device=dev) if slots else None
         C_indptr = torch.empty(A_rows + 1, dtype=torch.int64, device=dev)
-        _cabi.call("nb200_spgemm_symbolic", A_rows, A_cols, B_cols, _ptr(ai), _ptr(ap), _ptr(bi), _ptr(bp), itype,
-                   _ptr(work), wbytes, _ptr(spill), slots, _ptr(C_indptr), _stream())
-        head = _header(work)
-        if int(head[14]) != 0:
+
+        def count(spill, slots):
+            _cabi.call("nb200_spgemm_plan", A_rows, A_cols, plan_a.nnz, _ptr(ai), _ptr(ap), _ptr(bp), itype,
+                       _ptr(work), wbytes, _stream())
+            _cabi.call("nb200_spgemm_symbolic", A_rows, A_cols, B_cols, _ptr(ai), _ptr(ap), _ptr(bi), _ptr(bp), itype,
+                       _ptr(work), wbytes, _ptr(spill), slots, _ptr(C_indptr), _stream())
+            return _header(work)
+
+        # One host read per product: planning and the symbolic phase are enqueued together, without a
+        # spill area.  Only a matrix with rows of more than 4096 products needs one; the header then says
+        # how large, and the two steps run once more with it.
+        head = count(None, 0)
+        slots = int(head[_HDR_SYM_SPILL])
+        if slots > 0:
+            spill = torch.empty(slots * 4, dtype=torch.uint8, device=dev)
+            head = count(spill, slots)
+        if int(head[_HDR_ERROR]) != 0:
             raise RuntimeError("nb200_spgemm_symbolic: spill area too small")
-        nnz_c, slots = int(head[13]), int(head[12])
+        nnz_c, slots = int(head[_HDR_NNZ]), int(head[_HDR_NUM_SPILL])
         spill = torch.empty(slots * (vbytes + 4), dtype=torch.uint8, device=dev) if slots else None
         C_indices = torch.empty(nnz_c, dtype=torch.int64, device=dev)
         C_data = torch.empty(nnz_c, dtype=A_data.dtype, device=dev)

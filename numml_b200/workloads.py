@@ -57,9 +57,10 @@ def _stencil(dims, offsets, diag_val, off_val, dtype, lower_only=False, row_rang
     return vals.contiguous(), cols.contiguous(), indptr, (n, ntot)
 
 
-def poisson2d_5pt(n, dtype=torch.float32):
-    """5-point Laplacian on an n x n grid: 4 on the diagonal, -1 off; nnz = 5n^2 - 4n."""
-    return _stencil((n, n), [(-1, 0), (0, -1), (0, 1), (1, 0)], 4.0, -1.0, dtype)
+def poisson2d_5pt(n, dtype=torch.float32, row_range=None):
+    """5-point Laplacian on an n x n grid: 4 on the diagonal, -1 off; nnz = 5n^2 - 4n.
+    ``row_range`` builds a block of rows only (global columns)."""
+    return _stencil((n, n), [(-1, 0), (0, -1), (0, 1), (1, 0)], 4.0, -1.0, dtype, row_range=row_range)
 
 
 def poisson3d_7pt(n, dtype=torch.float64, nz=None, row_range=None):
@@ -148,6 +149,22 @@ def random_triangular(n, density, lower=True, seed=0, dtype=torch.float64, diag=
     vals = rng.standard_normal(len(c)) / np.sqrt(np.repeat(np.maximum(counts, 1), counts))
     vals[r == c] = diag
     return _pack(vals, c, indptr, (n, n), dtype)
+
+
+def row_block(data, indices, indptr, lo, hi):
+    """Rows lo..hi-1 of a CSR matrix as a CSR matrix of their own (columns unchanged)."""
+    a, b = int(indptr[lo]), int(indptr[hi])
+    return data[a:b].contiguous(), indices[a:b].contiguous(), (indptr[lo:hi + 1] - a).contiguous()
+
+
+def rows_subset(data, indices, indptr, rows):
+    """The given rows (a 1-D int64 tensor, any order) of a CSR matrix as a CSR matrix of their own,
+    plus the storage position in the original arrays of every entry taken."""
+    lens = (indptr[1:] - indptr[:-1])[rows]
+    ptr = torch.zeros(rows.numel() + 1, dtype=torch.int64)
+    torch.cumsum(lens, 0, out=ptr[1:])
+    pos = torch.repeat_interleave(indptr[rows] - ptr[:-1], lens) + torch.arange(int(ptr[-1]))
+    return data[pos].contiguous(), indices[pos].contiguous(), ptr, pos
 
 
 def randn(shape, seed, dtype):

@@ -12,8 +12,8 @@ clashes with this package's own operator module.  Output goes to ``oracle/_ref/`
 reference source is copied.
 
 Usage:  python oracle/build_ref.py [--reference /path/to/reference] [--force]
-The reference checkout is looked for at --reference, else at $NUMML_REFERENCE, else at the
-default location of the build machine.
+The reference checkout is looked for at --reference, else at $NUMML_REFERENCE, else in a directory
+named ``reference`` beside this repository.
 """
 import argparse
 import os
@@ -24,7 +24,8 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 MODULE = "numml_ref_cpp"
-DEFAULT_REFERENCE = os.environ.get("NUMML_REFERENCE", os.path.join(os.sep, "root", "reference"))
+DEFAULT_REFERENCE = os.environ.get("NUMML_REFERENCE",
+                                   os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 
 def ref_module_path():

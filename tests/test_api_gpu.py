@@ -289,6 +289,58 @@ def test_library_cg_loop_vs_oracle(sp, oracle, dtype, tol, with_x0):
     assert xt.requires_grad
 
 
+def test_cg_exact_convergence_stops_like_the_reference(sp):
+    """With rtol = 0 the reference's loop still ends when the residual reaches exactly zero.  On the
+    identity CG converges in one step; the remaining iterations must not turn x into NaN, and the
+    history must end at its first zero."""
+    import numml_b200.krylov as kry
+    n = 300
+    A = sp.eye(n, dtype=torch.float64).to(gpu)
+    b = W.randn(n, 5, torch.float64).to(gpu)
+    x, hist = kry.conjugate_gradient(A, b, rtol=0.0, iterations=6)
+    assert_same(b, x, "x")
+    assert hist.numel() == 2 and float(hist[1]) == 0.0 and float(hist[0]) > 0
+    Ag = A.copy()
+    Ag.requires_grad = True                      # the torch-op loop
+    x2, hist2 = kry.conjugate_gradient(Ag, b, rtol=0.0, iterations=6)
+    assert_same(b, x2.detach(), "x (torch-op loop)")
+    assert hist2.numel() == 2
+
+
+def test_conjugate_residual_vs_cpu_recurrence(sp, oracle):
+    """Conjugate residuals on a symmetric indefinite matrix (a shifted Laplacian), against the same
+    recurrence (reference numml/krylov.py:40-80) evaluated on the CPU with the oracle SpMV."""
+    import numml_b200.krylov as kry
+    d, i, p, (m, n) = W.poisson3d_7pt(10, torch.float64)
+    rows = torch.repeat_interleave(torch.arange(m), p[1:] - p[:-1])
+    d = d - 2.5 * (rows == i).double()           # eigenvalues on both sides of zero
+    b = W.randn(m, 6, torch.float64)
+    mv = lambda v: oracle.spgemv_forward(m, n, d, i, p, v)  # noqa: E731
+    iters = 30
+    x, r = torch.zeros(m, dtype=torch.float64), b.clone()
+    pv, Ar = r.clone(), mv(r)
+    Ap, hist = Ar.clone(), [tla.norm(r)]
+    for _ in range(iters):
+        alpha = (r @ Ar) / (Ap @ Ap)
+        x = x + alpha * pv
+        r_new = r - alpha * Ap
+        Ar_new = mv(r_new)
+        beta = (r_new @ Ar_new) / (r @ Ar)
+        pv = r_new + beta * pv
+        Ap = Ar_new + beta * Ap
+        Ar, r = Ar_new, r_new
+        hist.append(tla.norm(r))
+    A = sp.SparseCSRTensor((d, i, p), (m, n)).to(gpu)
+    xg, hg = kry.conjugate_residual(A, b.to(gpu), rtol=0.0, iterations=iters)
+    assert isinstance(hg, list) and len(hg) == iters + 1
+    assert_close(x, xg, "x", tol=1e-8)
+    assert_close(torch.stack(hist), torch.stack(hg), "residual history", tol=1e-8)
+    # with a preconditioner (a LinearOperator, as in the reference) the loop runs and reduces the residual
+    M = sp.LinearOperator((m, n), rm=lambda v: v / 4.0, lm=lambda v: v / 4.0)
+    _, hp = kry.conjugate_residual(A, b.to(gpu), M=M, rtol=1e-3, iterations=200)
+    assert float(hp[-1]) < float(hp[0])
+
+
 # ---------------------------------------------------------------------------------------------
 # Malformed structure raises instead of reading out of bounds or answering wrongly
 # ---------------------------------------------------------------------------------------------

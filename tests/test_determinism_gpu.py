@@ -1,7 +1,8 @@
 """Kernels that use no floating-point atomics must return the same bits on every run: each is run
-twice on the same inputs and the outputs are compared exactly.  (The SpGEMM forward accumulates
-colliding products with atomics and is excluded: its structure is exact, its values are not
-order-stable in the last bit.)"""
+twice on the same inputs and the outputs are compared exactly.  The SpGEMM forward is included for
+rows of at most 32 products, which one warp forms without a table and sums in the reference's
+order (the stencil and Galerkin products of the benchmark configuration); rows that go through the
+hash tables accumulate colliding products with atomics and are order-stable only in structure."""
 import pytest
 import torch
 
@@ -46,6 +47,7 @@ def test_stencil_kernels_solves_and_cg_are_run_to_run_identical():
     A = W.poisson2d_5pt(48, torch.float64)
     Ad = [t.cuda() for t in A[:3]]
     n = 48 * 48
+    _twice(lambda: ops.spgemm_forward(n, n, *Ad, n, n, *Ad))                # every row has at most 25 products
     C = ops.spgemm_forward(n, n, *Ad, n, n, *Ad)
     gC = W.randn(C[0].numel(), 6, torch.float64).cuda()
     _twice(lambda: ops.spgemm_backward(gC, C[1], C[2], n, n, *Ad, n, n, *Ad))

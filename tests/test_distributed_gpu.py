@@ -41,17 +41,44 @@ def _worker(rank, world, init_file):
         assert torch.equal(y.detach().cpu(), y_ref[lo:hi])
         assert torch.equal(A.data.grad.cpu(), gA_ref[sl])
         assert torch.allclose(xl.grad.cpu(), gx_ref[lo:hi], rtol=1e-13, atol=1e-13)
-        # the pre-planned engine (overlapped exchange, sub-range launches) gives the same results
-        eng = nd.DistSpMVEngine(A)
-        assert eng.fused                      # symmetric stencil block: one-pass backward over ghost rows
-        eng.x_ext[:hi - lo] = x[lo:hi].to(dev)
-        for _ in range(2):
-            y2 = eng.forward()
-            gA2, gx2 = eng.backward(g[lo:hi].to(dev))
-        assert torch.equal(y2.cpu(), y_ref[lo:hi])
-        assert torch.equal(gA2.cpu(), gA_ref[sl])
-        assert torch.allclose(gx2.cpu(), gx_ref[lo:hi], rtol=1e-13, atol=1e-13)
-        assert int(eng.status.item()) == 0
+        # the pre-planned engine (overlapped exchange, sub-range launches) gives the same results, with the
+        # halo values exchanged by NCCL and read from the neighbour's memory by the library's own kernels
+        results = {}
+        for exchange in ("nccl", "peer"):
+            eng = nd.DistSpMVEngine(A, exchange=exchange)
+            assert eng.fused                  # symmetric stencil block: one-pass backward over ghost rows
+            assert (eng.peer is not None) == (exchange == "peer")
+            eng.set_inputs(x[lo:hi].to(dev), g[lo:hi].to(dev))
+            dist.barrier()
+            for _ in range(3):                # both halves of the exchange buffers get reused
+                eng.step()
+            replay = eng.capture()
+            replay()
+            torch.cuda.synchronize()
+            assert torch.equal(eng.y.cpu(), y_ref[lo:hi])
+            assert torch.equal(eng.grad_A.cpu(), gA_ref[sl])
+            assert torch.allclose(eng.grad_x.cpu(), gx_ref[lo:hi], rtol=1e-13, atol=1e-13)
+            assert int(eng.status.item()) == 0
+            results[exchange] = eng.grad_x.clone()
+            if exchange == "peer":            # CG through the same engine against the CPU recurrence
+                b = W.randn(m, 5, torch.float64)
+                xs, hist = nd.DistCG(eng).solve(b[lo:hi].to(dev), 15)
+                xr, r = torch.zeros(m, dtype=torch.float64), b.clone()
+                pv, rz, ref = r.clone(), r @ r, []
+                ref.append(rz.sqrt())
+                for _ in range(15):
+                    Ap = oracle.spgemv_forward(m, n, d, i, p, pv)
+                    alpha = rz / (Ap @ pv)
+                    xr, r = xr + alpha * pv, r - alpha * Ap
+                    rz_new = r @ r
+                    pv, rz = r + (rz_new / rz) * pv, rz_new
+                    ref.append(rz.sqrt())
+                assert torch.allclose(hist.cpu(), torch.stack(ref), rtol=1e-9)
+                assert torch.allclose(xs.cpu(), xr[lo:hi], rtol=1e-8, atol=1e-10)
+                assert int(eng.status.item()) == 0
+            eng.close()
+        # both exchanges add the neighbours' partial sums in the same order
+        assert torch.equal(results["nccl"], results["peer"])
         Cd, Ci, Cp = A @ A
         C_ref = oracle.spgemm_forward(m, n, d, i, p, m, n, d, i, p)
         assert torch.equal(Cp.cpu(), C_ref[2][lo:hi + 1] - C_ref[2][lo])

@@ -67,6 +67,40 @@ def test_random_vs_oracle(oracle, ops, dtype, shapes, dens):
     assert_same(gB_ref, gB, "grad_B")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_small_rows_are_bit_exact(oracle, ops, dtype):
+    """Rows with at most 32 products (and at most 32 entries in the row of A) are formed by one warp
+    in the reference's order of additions: values bit for bit, including duplicates-heavy rows, rows of
+    A that select empty rows of B, rows with exactly 32 products, and rows just above the limit (which
+    take the hash path and are compared at the tolerance)."""
+    import numpy as np
+    rng = np.random.default_rng(3)
+    bm, bn = 500, 40                                     # few columns: many colliding products
+    lens_b = rng.integers(0, 9, size=bm)
+    lens_b[rng.choice(bm, 60, replace=False)] = 0        # empty rows of B
+    b_ptr = np.concatenate(([0], np.cumsum(lens_b)))
+    b_idx = np.concatenate([np.sort(rng.choice(bn, k, replace=False)) for k in lens_b] + [np.zeros(0, dtype=np.int64)])
+    B = (torch.from_numpy(rng.standard_normal(len(b_idx))).to(dtype), torch.from_numpy(b_idx.astype(np.int64)),
+         torch.from_numpy(b_ptr.astype(np.int64)), (bm, bn))
+    am = 3000
+    lens_a = rng.integers(0, 7, size=am)
+    a_ptr = np.concatenate(([0], np.cumsum(lens_a)))
+    a_idx = np.concatenate([np.sort(rng.choice(bm, k, replace=False)) for k in lens_a] + [np.zeros(0, dtype=np.int64)])
+    A = (torch.from_numpy(rng.standard_normal(len(a_idx))).to(dtype), torch.from_numpy(a_idx.astype(np.int64)),
+         torch.from_numpy(a_ptr.astype(np.int64)), (am, bm))
+    products = np.array([lens_b[a_idx[a_ptr[r]:a_ptr[r + 1]]].sum() for r in range(am)])
+    assert (products == 32).any() or (products > 32).any()
+    Cd_ref, Ci_ref, Cp_ref = oracle.spgemm_forward(am, bm, *A[:3], bm, bn, *B[:3])
+    (Cd, Ci, Cp), _ = run_case(ops, A, B)
+    assert_same(Cp_ref, Cp, "C_indptr")
+    assert_same(Ci_ref, Ci, "C_indices")
+    assert_close(Cd_ref, Cd, "C_data")
+    rows = torch.repeat_interleave(torch.arange(am), Cp_ref[1:] - Cp_ref[:-1])
+    small = torch.from_numpy(products <= 32)[rows]
+    assert int(small.sum()) > 0 and int((~small).sum()) > 0
+    assert_same(Cd_ref[small], Cd.cpu()[small], "values of the rows formed by one warp")
+
+
 def test_empty_operands(ops):
     z = (torch.zeros(0, dtype=torch.float64), torch.zeros(0, dtype=torch.int64), torch.zeros(5, dtype=torch.int64), (4, 3))
     B = W.random_csr(3, 6, 0.5, seed=1, dtype=torch.float64, empty_rows=False)
@@ -87,7 +121,7 @@ def test_galerkin_product_vs_oracle(oracle, ops):
     ref = oracle.spgemm_forward(am, an, *A[:3], am, an, *A[:3])
     assert ref[0].numel() == 13 * n * n - 20 * n + 4
     (Cd, Ci, Cp), _ = run_case(ops, A, A)
-    assert_same(ref[2], Cp, "AA indptr"); assert_same(ref[1], Ci, "AA indices"); assert_close(ref[0], Cd, "AA data")
+    assert_same(ref[2], Cp, "AA indptr"); assert_same(ref[1], Ci, "AA indices"); assert_same(ref[0], Cd, "AA data")
     # Pt = P^T, then (Pt A) P
     Pt_ref = oracle.csr_transpose_forward(pm, pn, *P[:3])
     Pt = (Pt_ref[0], Pt_ref[1], Pt_ref[2], (pn, pm))

@@ -267,13 +267,56 @@ def test_row_range_entry_points(oracle):
 
     assert plan.pattern_symmetric()
     _, _, t_perm, _ = plan.transpose()
-    gA = torch.full_like(dd, float("nan"))
-    gx = torch.full_like(dx, float("nan"))
     cut = 4096                                  # two launches: rows [cut, m) first, then [0, cut)
-    for lo, hi in ((cut, m), (0, cut)):
-        _cabi.call("nb200_spgemv_backward_symmetric_rows", m, d.numel(), lo, hi, _cabi_ptr(dd), _cabi_ptr(idx),
-                   _cabi_ptr(ptr), _cabi_ptr(t_perm), _cabi_ptr(dx), _cabi_ptr(dg), _cabi_ptr(gA), _cabi_ptr(gx), 256,
-                   _cabi_ptr(status), _cabi.F64, itype, stream)
-    assert_same(gA_ref, gA, "grad_A (fused, two row ranges)")
-    assert_same(gx_ref, gx, "grad_x (fused, two row ranges)")
+    # once with values that differ from their mirror images (general pass), once with values made
+    # symmetric (d[k] + d[mirror of k]: the same bits on both sides) and the value-symmetric pass
+    d_sym = d + d[t_perm.cpu().long()]
+    for values_symmetric, vals in ((0, d), (1, d_sym)):
+        gA_ref, gx_ref = oracle.spgemv_backward(g, m, k, vals, i, p, x)
+        dv = vals.cuda()
+        word = torch.zeros(1, dtype=torch.int32, device="cuda")
+        _cabi.call("nb200_csr_values_symmetric", d.numel(), _cabi_ptr(dv), _cabi_ptr(t_perm), _cabi_ptr(word),
+                   _cabi.F64, itype, stream)
+        assert int(word.item()) == (0 if values_symmetric else 1)
+        gA = torch.full_like(dd, float("nan"))
+        gx = torch.full_like(dx, float("nan"))
+        for lo, hi in ((cut, m), (0, cut)):
+            _cabi.call("nb200_spgemv_backward_symmetric_rows", m, d.numel(), lo, hi, _cabi_ptr(dv), _cabi_ptr(idx),
+                       _cabi_ptr(ptr), _cabi_ptr(t_perm), _cabi_ptr(dx), _cabi_ptr(dg), _cabi_ptr(gA), _cabi_ptr(gx),
+                       values_symmetric, 256, _cabi_ptr(status), _cabi.F64, itype, stream)
+        assert_same(gA_ref, gA, f"grad_A (fused, two row ranges, values_symmetric={values_symmetric})")
+        assert_same(gx_ref, gx, f"grad_x (fused, two row ranges, values_symmetric={values_symmetric})")
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_value_symmetric_backward_is_chosen_only_when_it_applies(oracle, dtype):
+    """The operator switches to the value-symmetric pass on the second call with unchanged values, and
+    only if the device-side test finds the matrix equal to its transpose bit for bit; an in-place
+    change of one value (version bump) sends it back to the general pass.  Results are bit-exact
+    against the oracle in every state."""
+    from numml_b200 import numml_torch_cpp as ops, _plan
+    gen = W.poisson2d_5pt if dtype == torch.float32 else W.poisson3d_7pt
+    d, i, p, (m, k) = gen(48 if dtype == torch.float32 else 24, dtype)
+    x, g = W.randn(k, 0, dtype), W.randn(m, 1, dtype)
+    dd, di, dp, dx, dg = [t.cuda() for t in (d, i, p, x, g)]
+    plan = _plan.get_plan(m, k, di, dp)
+
+    def check(vals_cpu, vals_dev, expect_symmetric):
+        gA_ref, gx_ref = oracle.spgemv_backward(g, m, k, vals_cpu, i, p, x)
+        gA, gx = ops.spgemv_backward(dg, m, k, vals_dev, di, dp, dx)
+        assert_same(gA_ref, gA, "grad_A")
+        assert_same(gx_ref, gx, "grad_x")
+        state = plan.extra["values_symmetric"]
+        assert state[1] is expect_symmetric, state[:2]
+
+    check(d, dd, None)            # first sighting of these values: general pass, nothing tested yet
+    check(d, dd, True)            # second sighting: tested, symmetric -> value-symmetric pass from now on
+    check(d, dd, True)
+    with torch.no_grad():         # break the symmetry of one off-diagonal pair in place
+        dd[1] += 0.5
+    d2 = dd.cpu()
+    check(d2, dd, None)
+    check(d2, dd, False)          # tested, not symmetric: stays on the general pass
+    check(d2, dd, False)
+    ops.check_status()
