@@ -456,7 +456,7 @@ def single_gpu_spmv(n, dev, ops):
     return step_dev, step_e2e, info
 
 
-def slab_engine(n, nz_total, ctx, ops):
+def slab_engine(n, nz_total, ctx, ops, exchange="auto"):
     """A DistSpMVEngine over this rank's slab of the n x n x nz_total grid (z-planes split evenly)."""
     from numml_b200 import distributed as nd, workloads as W
     plane = n * n
@@ -464,7 +464,30 @@ def slab_engine(n, nz_total, ctx, ops):
     lo, hi = bounds[ctx.rank], bounds[ctx.rank + 1]
     d, i, p, _ = W.poisson3d_7pt(n, torch.float64, nz=nz_total, row_range=(lo, hi))
     A = nd.DistSparseCSR(d.to(ctx.dev), i.to(ctx.dev), p.to(ctx.dev), (plane * nz_total,) * 2, bounds, ops=ops)
-    return nd.DistSpMVEngine(A), A, bounds, (d, i, p)
+    return nd.DistSpMVEngine(A, exchange=exchange), A, bounds, (d, i, p)
+
+
+def checked_slab_engine(n, nz_total, ctx, ops, x_seed, g_seed):
+    """slab_engine whose first step has been compared with the oracle on every rank.  The peer-memory
+    exchange is tried first; if a step over it does not reproduce the oracle (or a wait runs out) on any
+    rank, every rank falls back to the NCCL exchange together and the check is repeated.  Returns
+    (engine, A, bounds, csr, report) or raises SystemExit when neither exchange verifies."""
+    report = {}
+    for exchange in ("auto", "nccl"):
+        engine, A, bounds, csr = slab_engine(n, nz_total, ctx, ops, exchange)
+        engine.set_inputs(slab_vectors(bounds, ctx.rank, x_seed).to(ctx.dev), slab_vectors(bounds, ctx.rank, g_seed).to(ctx.dev))
+        report = {}
+        ok = verify_slab(ctx, n, nz_total, bounds, engine, x_seed, g_seed, report)
+        ok = ok and int(engine.status.item()) == 0
+        if ctx.all_true(ok):
+            return engine, A, bounds, csr, report
+        print(f"rank {ctx.rank}: a step with exchange {engine.exchange!r} does not match the oracle: {report}", file=sys.stderr)
+        was_peer = engine.peer is not None
+        engine.status.zero_()
+        engine.close()
+        if not was_peer:
+            break
+    raise SystemExit(f"rank {ctx.rank}: one step does not match the CPU oracle: {report}")
 
 
 def slab_vectors(bounds, rank, seed_base):
@@ -492,6 +515,7 @@ def verify_slab(ctx, n, nz_total, bounds, engine, x_seed, g_seed, report):
     gA_all, gx_all = oracle.spgemv_backward(gg[a:b].contiguous(), b - a, total, d, i, p, xg)
     ea, eb = int(p[lo - a]), int(p[hi - a])
     engine.y.fill_(float("nan")); engine.grad_A.fill_(float("nan"))
+    ctx.barrier()                                  # the ranks step together: a neighbour's wait is bounded
     engine.step()
     torch.cuda.synchronize()
     ok = compare("y", y_ref, engine.y, 0.0, report)
@@ -501,22 +525,25 @@ def verify_slab(ctx, n, nz_total, bounds, engine, x_seed, g_seed, report):
     return ok
 
 
-def multi_gpu_spmv(n, ctx, ops, nz_total=None, label="weak"):
+def multi_gpu_spmv(n, ctx, ops, nz_total=None):
     """Step closures for N > 1: every rank owns a slab of the n x n x nz_total grid (default: n planes
-    per rank, i.e. one n^3 slab each)."""
+    per rank, i.e. one n^3 slab each).  The engine comes back verified against the oracle."""
     nz_total = n * ctx.world if nz_total is None else nz_total
-    engine, A, bounds, (d, i, p) = slab_engine(n, nz_total, ctx, ops)
+    engine, A, bounds, (d, i, p), verified = checked_slab_engine(n, nz_total, ctx, ops, 100, 200)
     rows = bounds[ctx.rank + 1] - bounds[ctx.rank]
     x_h, g_h = slab_vectors(bounds, ctx.rank, 100), slab_vectors(bounds, ctx.rank, 200)
-    engine.set_inputs(x_h.to(ctx.dev), g_h.to(ctx.dev))
     A.requires_grad = True
     step_dev, mode = engine.step, engine.schedule
     if os.environ.get("NB200_BENCH_GRAPH", "1") == "1":
         try:
+            ctx.barrier()
             step_dev, mode = engine.capture(), engine.schedule + ", one CUDA graph per step"
         except Exception as e:          # capture is an optimisation; the eager schedule is always valid
             print(f"rank {ctx.rank}: CUDA graph capture failed ({type(e).__name__}: {e}); running eager launches", file=sys.stderr)
             step_dev = engine.step
+    captured = ctx.all_true(step_dev is not engine.step)
+    if not captured:                    # every rank runs the same schedule
+        step_dev, mode = engine.step, engine.schedule
 
     x_pin, g_pin = x_h.pin_memory(), g_h.pin_memory()
     y_pin = torch.empty(rows, dtype=torch.float64).pin_memory()
@@ -536,7 +563,8 @@ def multi_gpu_spmv(n, ctx, ops, nz_total=None, label="weak"):
         torch.cuda.current_stream().synchronize()
 
     def verify(report):
-        return verify_slab(ctx, n, nz_total, bounds, engine, 100, 200, report)
+        report.update(verified)
+        return True
 
     info = {"nnz": int(d.numel()), "rows": rows, "cols": engine.n_ext, "status_word": engine.status, "schedule": mode,
             "kernels": ("tma-pipelined, fused backward over ghost rows" if engine.fused else "tma-pipelined") if engine.br else "register-staged",
@@ -556,15 +584,15 @@ def extra_strong(ctx, ops, n, peak, steps, min_timed_s):
         return None                                # identical to the headline at one GPU
     if n % ctx.world != 0:
         return {"skipped": f"{n} planes do not split evenly over {ctx.world} ranks"}
-    step_dev, _, info = multi_gpu_spmv(n, ctx, ops, nz_total=n, label="strong")
+    step_dev, _, info = multi_gpu_spmv(n, ctx, ops, nz_total=n)
     report = {}
-    if not ctx.all_true(info["verify"](report)):
-        return {"error": "mismatch against the oracle", "verified": report}
+    info["verify"](report)
     t = timed_blocks(ctx, step_dev, steps, 5, min_timed_s)
     rows, nnz = n ** 3, 7 * n ** 3 - 6 * n ** 2
     fwd_b, bwd_b = algorithmic_bytes(rows, rows, nnz, 8, INDEX_BYTES_CREDITED)
     gbs = (fwd_b + bwd_b) / (t["ms_per_step"] * 1e-3) / 1e9
     phases = info["engine"].phase_times() if hasattr(info["engine"], "phase_times") else None
+    info["engine"].close()
     return {"workload": f"poisson3d_7pt_{n}^3_fp64 split over {ctx.world} GPUs", "ms_per_step": t["ms_per_step"], "GBps": gbs,
             "frac_of_aggregate_peak": gbs / (peak * ctx.world), "blocks": t["blocks"], "schedule": info["schedule"],
             "exchange": info["exchange"], "phases_us": phases, "verified": report}
@@ -589,7 +617,7 @@ def extra_cg(ctx, ops, n, peak):
         from numml_b200 import distributed as nd
         if n % ctx.world != 0:
             return {"skipped": f"{n} planes do not split evenly over {ctx.world} ranks"}
-        engine, A, bounds, _ = slab_engine(n, n, ctx, ops)
+        engine, A, bounds, _, _ = checked_slab_engine(n, n, ctx, ops, 100, 200)
         b = b_h[bounds[ctx.rank]:bounds[ctx.rank + 1]].to(ctx.dev)
         solver = nd.DistCG(engine)
         solve = lambda: solver.solve(b, iters)  # noqa: E731
@@ -615,8 +643,12 @@ def extra_cg(ctx, ops, n, peak):
         ok = compare("residual_history_101", torch.stack(ref), hist, 1e-8, report)
         report["tolerance"] = "1e-8 (dot products reduced in another order than on the CPU)"
     if not ctx.all_true(ok):
+        if ctx.world > 1:
+            engine.close()
         return {"error": "mismatch against the oracle recurrence", "verified": report}
     ms = median_ms(ctx, solve, reps=5, warm=1)
+    if ctx.world > 1:
+        engine.close()
     fwd_b, _ = algorithmic_bytes(rows, rows, nnz, 8, INDEX_BYTES_CREDITED)
     bytes_ = iters * (fwd_b + 7 * rows * 8)
     return {"workload": f"100 CG iterations, poisson3d_7pt_{n}^3_fp64" + (f" split over {ctx.world} GPUs" if ctx.world > 1 else ""),
@@ -908,7 +940,9 @@ def run(args, ctx, ops, peak, peak_kind):
         result["roofline"] = info["roofline"](peak, peak_kind)
         if not args.no_cpu_baseline:
             result["cpu_baseline"] = cpu_baseline(n)
-    info.pop("engine", None)
+    engine = info.pop("engine", None)
+    if engine is not None:
+        engine.close()
     if not args.no_extras:
         result["extra"] = run_extras(ctx, ops, args, peak)
     return result

@@ -370,6 +370,50 @@ NB200_API int nb200_cg_fixed_iterations(int64_t n, int64_t nnz, const void* data
                                         int dtype, int itype, nb200_stream stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Pattern-building operators (all index arrays int64, as the matrices store them).  Each produces a new
+ * pattern in two steps: a count call that writes the new row pointers (the caller reads the last one, a
+ * device-to-host copy of 8 bytes, to size the outputs) and a fill call.  `workspace` must hold
+ * nb200_pattern_workspace_bytes(rows) bytes.
+ *
+ * nb200_csr_triangle_*   entries (r, c) with c <= r + k (lower != 0) or c >= r + k (lower == 0), in storage
+ *                        order: tril / triu of the reference (numml/sparse/_csr.py:234-330, Python loops
+ *                        there; its tril stops at the first entry beyond the bound, which is the same thing
+ *                        for rows with ascending columns).  `out_pos[q]` is the position in A of output
+ *                        entry q, with which the backward pass scatters gradients.
+ * nb200_csr_lincomb_*    C = alpha A + beta B on the union of the two patterns by a two-pointer merge of
+ *                        every row (columns ascending in both): replaces splincomb_forward / _backward
+ *                        (cpp/sparse_csr.hpp:66-78, CPU cpp/sparse_csr_cpu.cpp:387-560, CUDA
+ *                        cpp/sparse_csr_cuda.cu:303-540).  Values are formed as the reference forms them
+ *                        (alpha a, beta b, or alpha a + beta b with unfused multiply and add): bit-identical.
+ *                        Backward: grad_A[e] = grad_C[position of e's column in C] * alpha, same for B.
+ * nb200_coo_to_csr       stable sort of n COO entries by (row, column) -- or by row only when
+ *                        sort_columns == 0 -- as `perm` (perm[q] = index of the entry that comes q-th)
+ *                        and the row pointers: coo_to_csr of the reference (numml/sparse/_csr.py:78-99).
+ *                        Needs n, nrows, ncols < 2^31 and nb200_coo_workspace_bytes(n) bytes.
+ * ------------------------------------------------------------------------------------------- */
+NB200_API size_t nb200_pattern_workspace_bytes(int64_t rows);
+NB200_API int nb200_csr_triangle_count(int64_t rows, const int64_t* indices, const int64_t* indptr, int64_t k, int lower,
+                                       int64_t* out_indptr, void* workspace, size_t workspace_bytes, nb200_stream stream);
+NB200_API int nb200_csr_triangle_fill(int64_t rows, const void* data, const int64_t* indices, const int64_t* indptr,
+                                      int64_t k, int lower, const int64_t* out_indptr, void* out_data,
+                                      int64_t* out_indices, int64_t* out_pos, int dtype, nb200_stream stream);
+NB200_API int nb200_csr_lincomb_count(int64_t rows, const int64_t* A_indices, const int64_t* A_indptr,
+                                      const int64_t* B_indices, const int64_t* B_indptr, int64_t* C_indptr,
+                                      void* workspace, size_t workspace_bytes, nb200_stream stream);
+NB200_API int nb200_csr_lincomb_fill(int64_t rows, double alpha, const void* A_data, const int64_t* A_indices,
+                                     const int64_t* A_indptr, double beta, const void* B_data, const int64_t* B_indices,
+                                     const int64_t* B_indptr, const int64_t* C_indptr, void* C_data, int64_t* C_indices,
+                                     int dtype, nb200_stream stream);
+NB200_API int nb200_csr_lincomb_backward(int64_t rows, double alpha, const int64_t* A_indices, const int64_t* A_indptr,
+                                         double beta, const int64_t* B_indices, const int64_t* B_indptr,
+                                         const void* grad_C, const int64_t* C_indices, const int64_t* C_indptr,
+                                         void* grad_A, void* grad_B, int dtype, nb200_stream stream);
+NB200_API size_t nb200_coo_workspace_bytes(int64_t n);
+NB200_API int nb200_coo_to_csr(int64_t n, const int64_t* row_ind, const int64_t* col_ind, int64_t nrows, int64_t ncols,
+                               int sort_columns, int64_t* perm, int64_t* indptr, void* workspace, size_t workspace_bytes,
+                               nb200_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Halo exchange of a row-partitioned SpMV over peer memory.  No counterpart in the reference, which has
  * no multi-device path (its operators take whole matrices on one device, cpp/sparse_csr.hpp:32-105).
  *

@@ -427,3 +427,99 @@ def cg_fixed_iterations(A_rows, A_data, A_indices, A_indptr, b, x0, iterations):
                    _ptr(b), _ptr(x), int(x0 is not None), _ptr(hist), int(iterations), _ptr(work), wbytes,
                    _ptr(_status_word(dev)), code, itype, _stream())
     return x, hist
+
+
+# -------------------------------------------------------------------------------------------------
+# Pattern-building operators     reference cpp/sparse_csr.hpp:66-78, numml/sparse/_csr.py:78-99, 234-330
+# -------------------------------------------------------------------------------------------------
+def _pattern_workspace(rows, dev):
+    wbytes = _cabi.lib().nb200_pattern_workspace_bytes(rows)
+    return torch.empty(wbytes, dtype=torch.uint8, device=dev), wbytes
+
+
+def splincomb_forward(rows, cols, alpha, A_data, A_indices, A_indptr, beta, B_data, B_indices, B_indptr):
+    """C = alpha A + beta B on the union pattern (both operands with ascending columns per row).
+    ``alpha`` / ``beta`` are Python numbers or 0-d tensors, as in the reference."""
+    dev = _require_cuda(A_data, A_indices, A_indptr, B_data, B_indices, B_indptr)
+    A_data = _values(A_data)
+    B_data = _values(B_data, A_data)
+    A_indices, A_indptr = _index_tensor(A_indices), _index_tensor(A_indptr)
+    B_indices, B_indptr = _index_tensor(B_indices), _index_tensor(B_indptr)
+    _plan.get_plan(rows, cols, A_indices, A_indptr).require(sorted_columns=True, what="the linear combination")
+    _plan.get_plan(rows, cols, B_indices, B_indptr).require(sorted_columns=True, what="the linear combination")
+    alpha, beta = float(alpha), float(beta)
+    with _on(dev):
+        work, wbytes = _pattern_workspace(rows, dev)
+        C_indptr = torch.empty(rows + 1, dtype=torch.int64, device=dev)
+        _cabi.call("nb200_csr_lincomb_count", rows, _ptr(A_indices), _ptr(A_indptr), _ptr(B_indices), _ptr(B_indptr),
+                   _ptr(C_indptr), _ptr(work), wbytes, _stream())
+        nnz_c = int(C_indptr[-1].item())
+        C_data = torch.empty(nnz_c, dtype=A_data.dtype, device=dev)
+        C_indices = torch.empty(nnz_c, dtype=torch.int64, device=dev)
+        _cabi.call("nb200_csr_lincomb_fill", rows, alpha, _ptr(A_data), _ptr(A_indices), _ptr(A_indptr), beta, _ptr(B_data),
+                   _ptr(B_indices), _ptr(B_indptr), _ptr(C_indptr), _ptr(C_data), _ptr(C_indices), _dtype_code(A_data), _stream())
+    return [C_data, C_indices, C_indptr]
+
+
+def splincomb_backward(rows, cols, alpha, A_data, A_indices, A_indptr, beta, B_data, B_indices, B_indptr,
+                       grad_C_data, C_indices, C_indptr):
+    dev = _require_cuda(A_data, A_indices, A_indptr, B_data, B_indices, B_indptr, grad_C_data, C_indices, C_indptr)
+    grad_C = _values(grad_C_data, A_data)
+    with _on(dev):
+        # every entry of A and of B lies in the union pattern, so both gradients are written in full
+        grad_A = torch.empty_like(A_data)
+        grad_B = torch.empty_like(B_data)
+        _cabi.call("nb200_csr_lincomb_backward", rows, float(alpha), _ptr(_index_tensor(A_indices)), _ptr(_index_tensor(A_indptr)),
+                   float(beta), _ptr(_index_tensor(B_indices)), _ptr(_index_tensor(B_indptr)), _ptr(grad_C),
+                   _ptr(_index_tensor(C_indices)), _ptr(_index_tensor(C_indptr)), _ptr(grad_A), _ptr(grad_B),
+                   _dtype_code(A_data), _stream())
+    return [grad_A, grad_B]
+
+
+def csr_triangle(rows, cols, A_data, A_indices, A_indptr, k, lower):
+    """Entries on or below (``lower``) / on or above diagonal ``k``.  Returns ``[data, indices, indptr,
+    positions]``, the last being the position in A of every entry kept."""
+    dev = _require_cuda(A_data, A_indices, A_indptr)
+    A_data = _values(A_data)
+    A_indices, A_indptr = _index_tensor(A_indices), _index_tensor(A_indptr)
+    _plan.get_plan(rows, cols, A_indices, A_indptr)             # structure check: nothing may index out of bounds
+    with _on(dev):
+        work, wbytes = _pattern_workspace(rows, dev)
+        out_indptr = torch.empty(rows + 1, dtype=torch.int64, device=dev)
+        _cabi.call("nb200_csr_triangle_count", rows, _ptr(A_indices), _ptr(A_indptr), int(k), int(bool(lower)),
+                   _ptr(out_indptr), _ptr(work), wbytes, _stream())
+        n = int(out_indptr[-1].item())
+        out_data = torch.empty(n, dtype=A_data.dtype, device=dev)
+        out_indices = torch.empty(n, dtype=torch.int64, device=dev)
+        out_pos = torch.empty(n, dtype=torch.int64, device=dev)
+        _cabi.call("nb200_csr_triangle_fill", rows, _ptr(A_data), _ptr(A_indices), _ptr(A_indptr), int(k), int(bool(lower)),
+                   _ptr(out_indptr), _ptr(out_data), _ptr(out_indices), _ptr(out_pos), _dtype_code(A_data), _stream())
+    return [out_data, out_indices, out_indptr, out_pos]
+
+
+def scatter_into(dst, src, idx):
+    """dst[idx[k]] = src[k] for every k, in place (``idx`` int64 without repeats); returns ``dst``."""
+    dev = _require_cuda(dst, src, idx)
+    with _on(dev):
+        _cabi.call("nb200_scatter", int(src.numel()), _ptr(_values(src, dst)), _ptr(_index_tensor(idx)), _ptr(dst),
+                   _dtype_code(dst), _cabi.I64, _stream())
+    return dst
+
+
+def coo_to_csr_order(row_ind, col_ind, nrows, ncols, sort_columns=True):
+    """``(perm, indptr)`` of the COO entries sorted stably by (row, column) -- by row only when
+    ``sort_columns`` is false: entry ``perm[q]`` comes q-th."""
+    dev = _require_cuda(row_ind, col_ind)
+    row_ind, col_ind = _index_tensor(row_ind), _index_tensor(col_ind)
+    n = int(row_ind.numel())
+    if n > 0 and (int(row_ind.min()) < 0 or int(row_ind.max()) >= nrows or int(col_ind.min()) < 0 or int(col_ind.max()) >= ncols):
+        raise RuntimeError(f"COO indices outside the matrix shape ({nrows}, {ncols})")
+    with _on(dev):
+        wbytes = _cabi.lib().nb200_coo_workspace_bytes(n)
+        work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+        perm = torch.empty(n, dtype=torch.int64, device=dev)
+        indptr = torch.empty(nrows + 1, dtype=torch.int64, device=dev)
+        _cabi.call("nb200_coo_to_csr", n, _ptr(row_ind), _ptr(col_ind), nrows, ncols, int(bool(sort_columns)), _ptr(perm),
+                   _ptr(indptr), _ptr(work), wbytes, _stream())
+    return perm, indptr
+

@@ -72,6 +72,10 @@ def coo_to_csr(values, row_ind, col_ind, shape, sort=True):
     (reference ``numml/sparse/_csr.py:78-99``)."""
     row_ind = row_ind.long()
     col_ind = col_ind.long()
+    if values.is_cuda and values.numel() > 0:
+        # one stable two-key radix sort on the device (order and row pointers together)
+        perm, indptr = numml_torch_cpp.coo_to_csr_order(row_ind, col_ind, int(shape[0]), int(shape[1]), sort_columns=sort)
+        return values[perm], col_ind[perm], indptr
     if sort and values.numel() > 0:
         order = torch.argsort(row_ind * int(shape[1]) + col_ind, stable=True)
         values, row_ind, col_ind = values[order], row_ind[order], col_ind[order]
@@ -207,8 +211,55 @@ class sprowsum(torch.autograd.Function):
 # ---------------------------------------------------------------------------------------------
 # Pattern helpers written with torch tensor ops (differentiable through `data`)
 # ---------------------------------------------------------------------------------------------
+class splincomb(torch.autograd.Function):
+    """alpha*A + beta*B on the union pattern (reference ``numml/sparse/_csr.py:187-232``), CUDA tensors."""
+
+    @staticmethod
+    def forward(ctx, shape, alpha, A_data, A_indices, A_indptr, beta, B_data, B_indices, B_indptr):
+        with Profiler('splincomb forward'):
+            C_data, C_indices, C_indptr = numml_torch_cpp.splincomb_forward(
+                shape[0], shape[1], alpha, A_data, A_indices, A_indptr, beta, B_data, B_indices, B_indptr)
+        ctx.save_for_backward(A_data, A_indices, A_indptr, B_data, B_indices, B_indptr, C_indices, C_indptr)
+        ctx.shape, ctx.alpha, ctx.beta = shape, alpha, beta
+        ctx.mark_non_differentiable(C_indices, C_indptr)
+        return C_data, C_indices, C_indptr
+
+    @staticmethod
+    def backward(ctx, grad_C_data, _gi, _gp):
+        A_data, A_indices, A_indptr, B_data, B_indices, B_indptr, C_indices, C_indptr = ctx.saved_tensors
+        with Profiler('splincomb backward'):
+            grad_A, grad_B = numml_torch_cpp.splincomb_backward(
+                ctx.shape[0], ctx.shape[1], ctx.alpha, A_data, A_indices, A_indptr, ctx.beta, B_data, B_indices, B_indptr,
+                grad_C_data.contiguous(), C_indices, C_indptr)
+        return None, None, grad_A, None, None, None, grad_B, None, None
+
+
+class sptriangle(torch.autograd.Function):
+    """tril / triu (reference ``numml/sparse/_csr.py:234-330``) on CUDA tensors; the backward scatters
+    the gradient of the kept entries back to their positions in A and leaves zeros elsewhere."""
+
+    @staticmethod
+    def forward(ctx, shape, A_data, A_indices, A_indptr, k, lower):
+        with Profiler('tril forward' if lower else 'triu forward'):
+            data, indices, indptr, pos = numml_torch_cpp.csr_triangle(shape[0], shape[1], A_data, A_indices, A_indptr, k, lower)
+        ctx.save_for_backward(pos)
+        ctx.nnz = A_data.numel()
+        ctx.mark_non_differentiable(indices, indptr)
+        return data, indices, indptr
+
+    @staticmethod
+    def backward(ctx, grad_data, _gi, _gp):
+        (pos,) = ctx.saved_tensors
+        grad_A = torch.zeros(ctx.nnz, dtype=grad_data.dtype, device=grad_data.device)
+        if pos.numel() > 0:
+            grad_A = numml_torch_cpp.scatter_into(grad_A, grad_data.contiguous(), pos)
+        return None, grad_A, None, None, None, None
+
+
 def _lincomb(shape, alpha, A, beta, B):
     """C = alpha*A + beta*B on the union pattern, columns ascending per row."""
+    if A.data.is_cuda and not isinstance(alpha, torch.Tensor) and not isinstance(beta, torch.Tensor):
+        return splincomb.apply(tuple(shape), alpha, A.data, A.indices, A.indptr, beta, B.data, B.indices, B.indptr)
     rows, cols = int(shape[0]), int(shape[1])
     ra, rb = _row_ids(A.indptr, A.nnz), _row_ids(B.indptr, B.nnz)
     keys = torch.cat((ra * cols + A.indices, rb * cols + B.indices))
@@ -222,6 +273,8 @@ def _lincomb(shape, alpha, A, beta, B):
 
 
 def _triangle(A, k, lower):
+    if A.data.is_cuda:
+        return SparseCSRTensor(sptriangle.apply(tuple(A.shape), A.data, A.indices, A.indptr, int(k), bool(lower)), A.shape, clone=False)
     r = _row_ids(A.indptr, A.nnz)
     keep = (A.indices <= r + k) if lower else (A.indices >= r + k)
     indptr = torch.zeros(A.shape[0] + 1, dtype=torch.long, device=A.indptr.device)

@@ -162,5 +162,45 @@ def sptrsv_backward(grad_x, x, rows, cols, data, indices, indptr, lower, unit, b
     return [grad_A, grad_b]
 
 
+def splincomb_forward(rows, cols, alpha, A_data, A_indices, A_indptr, beta, B_data, B_indices, B_indptr):
+    A_data, A_indices, A_indptr = _c(A_data), _c(A_indices, torch.int64), _c(A_indptr, torch.int64)
+    B_data, B_indices, B_indptr = _c(B_data), _c(B_indices, torch.int64), _c(B_indptr, torch.int64)
+    lib().oracle_splincomb_count.restype = ctypes.c_int64
+    C_indptr = torch.empty(rows + 1, dtype=torch.int64)
+    nnz = lib().oracle_splincomb_count(_i(rows), _p(A_indices), _p(A_indptr), _p(B_indices), _p(B_indptr), _p(C_indptr))
+    C_data = torch.empty(nnz, dtype=A_data.dtype)
+    C_indices = torch.empty(nnz, dtype=torch.int64)
+    scalar = ctypes.c_double if A_data.dtype == torch.float64 else ctypes.c_float
+    getattr(lib(), "oracle_splincomb_forward_" + _sfx(A_data))(
+        _i(rows), scalar(float(alpha)), _p(A_data), _p(A_indices), _p(A_indptr), scalar(float(beta)), _p(B_data),
+        _p(B_indices), _p(B_indptr), _p(C_data), _p(C_indices))
+    return [C_data, C_indices, C_indptr]
+
+
+def splincomb_backward(rows, cols, alpha, A_data, A_indices, A_indptr, beta, B_data, B_indices, B_indptr,
+                       grad_C, C_indices, C_indptr):
+    A_data, A_indices, A_indptr = _c(A_data), _c(A_indices, torch.int64), _c(A_indptr, torch.int64)
+    B_data, B_indices, B_indptr = _c(B_data), _c(B_indices, torch.int64), _c(B_indptr, torch.int64)
+    grad_C, C_indices, C_indptr = _c(grad_C), _c(C_indices, torch.int64), _c(C_indptr, torch.int64)
+    scalar = ctypes.c_double if A_data.dtype == torch.float64 else ctypes.c_float
+    fn = getattr(lib(), "oracle_splincomb_backward_" + _sfx(A_data))
+    grad_A, grad_B = torch.empty_like(A_data), torch.empty_like(B_data)
+    fn(_i(rows), scalar(float(alpha)), _p(A_indices), _p(A_indptr), _p(grad_C), _p(C_indices), _p(C_indptr), _p(grad_A))
+    fn(_i(rows), scalar(float(beta)), _p(B_indices), _p(B_indptr), _p(grad_C), _p(C_indices), _p(C_indptr), _p(grad_B))
+    return [grad_A, grad_B]
+
+
+def triangle(rows, data, indices, indptr, k, lower):
+    """tril (``lower``) / triu of a CSR matrix with ascending columns per row, as the reference's Python
+    loops compute it (numml/sparse/_csr.py:234-330): entries with column <= row + k (>= row + k), in
+    storage order.  Returns (data, indices, indptr, position in A of every entry kept)."""
+    data, indices, indptr = _c(data), _c(indices, torch.int64), _c(indptr, torch.int64)
+    row_of = torch.repeat_interleave(torch.arange(rows), indptr[1:] - indptr[:-1])
+    keep = (indices <= row_of + k) if lower else (indices >= row_of + k)
+    out_ptr = torch.zeros(rows + 1, dtype=torch.int64)
+    out_ptr[1:] = torch.cumsum(torch.bincount(row_of[keep], minlength=rows), 0)
+    return data[keep], indices[keep], out_ptr, torch.nonzero(keep).flatten()
+
+
 if __name__ == "__main__":
     print(build(force=True))

@@ -113,6 +113,45 @@ def test_port_matches_compiled_reference(oracle, reference_module, dtype):
                 assert_same(a, bb)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_pattern_operators_match_the_reference(oracle, reference_module, dtype):
+    """Linear combination on the union pattern against the compiled reference (forward and backward),
+    and tril / triu against a restatement of the reference's Python loops."""
+    d, i, p, (m, n) = W.random_csr(200, 150, 0.05, seed=201, dtype=dtype)
+    d2, i2, p2, _ = W.random_csr(200, 150, 0.07, seed=202, dtype=dtype)
+    C = oracle.splincomb_forward(m, n, 1.5, d, i, p, -0.25, d2, i2, p2)
+    gC = W.randn(C[0].numel(), 9, dtype)
+    gA, gB = oracle.splincomb_backward(m, n, 1.5, d, i, p, -0.25, d2, i2, p2, gC, C[1], C[2])
+    if reference_module is not None:
+        a, b = torch.tensor(1.5, dtype=dtype), torch.tensor(-0.25, dtype=dtype)
+        R = reference_module.splincomb_forward(m, n, a, d, i, p, b, d2, i2, p2)
+        for u, v in zip(R, C):
+            assert_same(u, v)
+        Rg = reference_module.splincomb_backward(m, n, a, d, i, p, b, d2, i2, p2, gC, C[1], C[2])
+        assert_same(Rg[0], gA)
+        assert_same(Rg[1], gB)
+    # the union pattern is sorted and holds every entry of both operands
+    rows = torch.repeat_interleave(torch.arange(m), C[2][1:] - C[2][:-1])
+    key = rows * n + C[1]
+    assert torch.all(key[1:] > key[:-1])
+    for k in (-2, 0, 3):
+        for lower in (True, False):
+            td, ti, tp, pos = oracle.triangle(m, d, i, p, k, lower)
+            ld, li, lp = [], [], [0]                       # the reference's loops, entry by entry
+            for r in range(m):
+                for e in range(int(p[r]), int(p[r + 1])):
+                    c = int(i[e])
+                    if lower and c > r + k:
+                        break
+                    if not lower and c < r + k:
+                        continue
+                    ld.append(float(d[e])); li.append(c)
+                lp.append(len(ld))
+            assert ti.tolist() == li and tp.tolist() == lp
+            assert_same(torch.tensor(ld, dtype=dtype), td)
+            assert torch.equal(d[pos], td)
+
+
 def test_workload_sizes():
     assert W.poisson2d_5pt(256)[0].numel() == 326656
     assert W.poisson3d_7pt(16)[0].numel() == 7 * 16 ** 3 - 6 * 16 ** 2
