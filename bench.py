@@ -776,7 +776,8 @@ def extra_spmm(ctx, ops, n, K, peak):
         Y_ref = oracle.spdmm_forward(rows_here.numel(), cols.numel(), sd, inv.contiguous(), sp_, X_full[cols.to(dev)].cpu())
         ok = compare("Y_rows", Y_ref, Y[(rows_here - row0).to(dev)], 0.0, report)
     report["sample"] = "4096 random rows of the graph, each checked by the rank that owns it"
-    del X_full
+    if ctx.world > 1:
+        X_full = None                               # only this rank's block (a copy) is used from here on
     if not ctx.all_true(ok):
         return {"error": "mismatch against the oracle", "verified": report}
     t_f = median_ms(ctx, fwd, reps=5, warm=2)

@@ -191,20 +191,23 @@ NB200_API int nb200_widen_indices(int64_t n, const int32_t* in32, int64_t* out64
  * `perm` (itype, may be NULL) as in nb200_spgemv_forward: with a transposed structure this call
  * computes grad_B = A^T grad_C of spdmm_backward without atomics.  128-bit loads are used when
  * K * sizeof(value) is a multiple of 16 and B, C are 16-byte aligned.
+ * `row_order` (rows int32, a permutation of the rows, may be NULL): the order in which rows are handed
+ * to lane groups.  Rows sorted by descending length make the few very long rows of a skewed matrix
+ * start first instead of trailing; results are unchanged (every row is still summed alone, in order).
  * ------------------------------------------------------------------------------------------- */
 NB200_API int nb200_spdmm_forward(int64_t rows, int64_t cols, int64_t K, int64_t nnz,
                                   const void* data, const void* indices, const void* indptr,
-                                  const void* perm, const void* B, void* C,
+                                  const void* perm, const int32_t* row_order, const void* B, void* C,
                                   int dtype, int itype, nb200_stream stream);
 
 /* ---------------------------------------------------------------------------------------------
  * SpMM backward, masked part: grad_A[k] = <grad_C[row(k), :], B[col(k), :]>.
  * Replaces the grad_A half of spdmm_backward (reference cpp/sparse_csr.hpp:87-91, CPU
  * cpp/sparse_csr_cpu.cpp:624-636, CUDA cpp/sparse_csr_cuda.cu:611-645); the grad_B half is
- * nb200_spdmm_forward on the transposed structure.
+ * nb200_spdmm_forward on the transposed structure.  `row_order` as in nb200_spdmm_forward.
  * ------------------------------------------------------------------------------------------- */
 NB200_API int nb200_spdmm_backward_grad_A(int64_t rows, int64_t cols, int64_t K, int64_t nnz,
-                                          const void* indices, const void* indptr,
+                                          const void* indices, const void* indptr, const int32_t* row_order,
                                           const void* B, const void* grad_C, void* grad_A,
                                           int dtype, int itype, nb200_stream stream);
 
@@ -278,13 +281,14 @@ NB200_API int nb200_spgemm_backward(int64_t A_rows, int64_t A_cols, int64_t A_nn
  * and, with the two helpers below, sptrsv_backward (cpp/sparse_csr.hpp:100-105, CPU :725-759,
  * CUDA :833-860).
  *
- * nb200_sptrsv_analyse   once per pattern and triangle: computes the dependency levels by frontier
- *                        peeling and writes `order` (n int32: rows sorted by level, then by row).
- *                        Needs the transposed structure of the matrix (t_indptr, t_indices; see
- *                        nb200_csr_transpose_structure) and columns sorted within each row.  The
- *                        number of levels is written to the HOST word *nlevels_host.  This call
- *                        synchronises `stream` (it polls a completion flag between batches of level
- *                        kernels); no kernel in it waits on another kernel.
+ * nb200_sptrsv_analyse   once per pattern and triangle: computes the dependency level of every row (one
+ *                        more than the largest level among the rows it depends on) in one launch, the
+ *                        level array serving as its own ready flag under bounded polls, and writes
+ *                        `order` (n int32: rows sorted by level, then by row).  Columns must be sorted
+ *                        within each row.  `t_indptr` / `t_indices` are not used (earlier versions peeled
+ *                        levels through the transposed structure) and may be NULL.  The number of levels
+ *                        is written to the HOST word *nlevels_host.  This call synchronises `stream` once.
+ *                        NB200_ERR_WAIT_BUDGET if a poll ran out (about two seconds without progress).
  * nb200_sptrsv_solve     x = A^{-1} b for `nrhs` right-hand sides stored row-major [n, nrhs] (nrhs = 1
  *                        is the reference's single-vector call).  Substitution is done in double and
  *                        rounded to the value type at the end, entries are accumulated in the

@@ -34,7 +34,7 @@ SIGNATURES = {
     "nb200_scatter": (_int, [_i64, _vp, _vp, _vp, _int, _int, _vp]),
     "nb200_narrow_indices": (_int, [_i64, _vp, _vp, _vp]),
     "nb200_widen_indices": (_int, [_i64, _vp, _vp, _vp]),
-    "nb200_spdmm_forward": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
+    "nb200_spdmm_forward": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
     "nb200_spgemm_workspace_bytes": (_sz, [_i64]),
     "nb200_spgemm_plan": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _int, _vp, _sz, _vp]),
     "nb200_spgemm_symbolic": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp, _sz, _vp, _i64, _vp, _vp]),
@@ -68,7 +68,7 @@ SIGNATURES = {
     "nb200_ipc_open": (_int, [_vp, _c.POINTER(_vp)]),
     "nb200_ipc_close": (_int, [_vp]),
     "nb200_ipc_free": (_int, [_vp]),
-    "nb200_spdmm_backward_grad_A": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
+    "nb200_spdmm_backward_grad_A": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
 }
 
 _lib = None

@@ -163,6 +163,24 @@ class PatternPlan:
             self.extra[key] = choice if self.nnz > 0 else 0
         return self.extra[key]
 
+    # -- row schedule for SpMM ------------------------------------------------------------------------
+    def spmm_row_order(self, transposed=False):
+        """int32 permutation of the rows (of the pattern, or of its transpose) by descending length, or
+        None when the lengths are even enough for the natural order (which keeps neighbouring rows, and
+        the dense rows they share, together).  Skewed matrices get it: a row of thousands of entries is
+        walked by one lane group alone and should start first, not last."""
+        key = ("spmm_row_order", bool(transposed))
+        if key not in self.extra:
+            ptr = self.transpose()[0] if transposed else self.indptr
+            rows = int(ptr.numel()) - 1
+            order = None
+            if rows >= 4096 and self.nnz > 0:
+                lens = ptr[1:] - ptr[:-1]
+                if int(lens.max()) > 16 * max(1.0, self.nnz / rows):
+                    order = torch.argsort(lens, descending=True, stable=True).to(torch.int32)
+            self.extra[key] = order
+        return self.extra[key]
+
     # -- triangular-solve schedules ----------------------------------------------------------------
     def sptrsv_order(self, lower, transposed=False):
         """(order, nlevels) for solving with this pattern (``transposed=False``) or with its

@@ -103,29 +103,41 @@ __global__ void spgemm_products_kernel(int64_t rows, const I* __restrict__ A_ind
 // Distribute rows into per-bin lists (warp-aggregated appends) and size the spill tables.
 // `products` is the array written by spgemm_products_kernel; `size_in` is that array again (symbolic
 // phase) or the exact nnz of every output row (numeric phase).
-__global__ void spgemm_classify_kernel(int64_t rows, const int32_t* __restrict__ size_in,
-                                       const int32_t* __restrict__ products, bool numeric,
-                                       int32_t* __restrict__ lists, int64_t* __restrict__ spill_off,
-                                       unsigned long long* __restrict__ header) {
+__global__ void __launch_bounds__(256)
+spgemm_classify_kernel(int64_t rows, const int32_t* __restrict__ size_in,
+                       const int32_t* __restrict__ products, bool numeric,
+                       int32_t* __restrict__ lists, int64_t* __restrict__ spill_off,
+                       unsigned long long* __restrict__ header) {
+    // appends are aggregated per warp (match.any), then per block (shared counters): one global atomic
+    // per block and bin instead of one per warp
+    __shared__ unsigned s_count[kBins];
+    __shared__ unsigned long long s_base[kBins];
     const int hb = numeric ? kHdrNumBins : 0;
     const int lane = threadIdx.x & 31;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    const int64_t rows_pad = (rows + 31) & ~(int64_t)31;
+    const int64_t rows_pad = ceil_div(rows, (int64_t)blockDim.x) * blockDim.x;
     for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < rows_pad; r += stride) {
+        if (threadIdx.x < kBins) s_count[threadIdx.x] = 0;
+        __syncthreads();
         const bool ok = r < rows;
         const int32_t size = ok ? size_in[r] : 0;
         int bin = kBins;
         if (ok) bin = products[r] <= kWarpRowMax ? 0 : hash_bin_of(size, numeric);
         const uint32_t peers = __match_any_sync(0xffffffffu, bin);
+        const int leader = __ffs(peers) - 1;
+        unsigned warp_off = 0;
+        if (ok && lane == leader) warp_off = atomicAdd(&s_count[bin], (unsigned)__popc(peers));
+        warp_off = __shfl_sync(0xffffffffu, warp_off, leader);
+        __syncthreads();
+        if (threadIdx.x < kBins && s_count[threadIdx.x] > 0)
+            s_base[threadIdx.x] = atomicAdd(header + hb + threadIdx.x, (unsigned long long)s_count[threadIdx.x]);
+        __syncthreads();
         if (ok) {
-            const int leader = __ffs(peers) - 1;
-            unsigned long long base = 0;
-            if (lane == leader) base = atomicAdd(header + hb + bin, (unsigned long long)__popc(peers));
-            base = __shfl_sync(peers, base, leader);
-            const int64_t pos = (int64_t)base + __popc(peers & ((1u << lane) - 1u));
+            const int64_t pos = (int64_t)s_base[bin] + warp_off + __popc(peers & ((1u << lane) - 1u));
             lists[(int64_t)bin * rows + pos] = (int32_t)r;
             if (bin == 4) spill_off[pos] = (int64_t)atomicAdd(header + hb + kHdrSymSpill, (unsigned long long)spill_table_size(size));
         }
+        __syncthreads();
     }
 }
 
@@ -135,26 +147,25 @@ __global__ void spgemm_classify_kernel(int64_t rows, const int32_t* __restrict__
 template <typename T, typename I>
 struct WarpRow {          // what the lanes hold about a row before its products are formed
     int64_t row;
-    int64_t b_begin;      // lane e < na: first position of the row of B that entry e of the row of A selects
+    int64_t a_begin;      // position of the row's first entry in A
+    I b_begin;            // lane e < na: first position of the row of B that entry e of the row of A selects
     int len;              // lane e < na: length of that row of B
     int na;               // entries of the row of A
-    T a_val;              // lane e < na: value of entry e (numeric phase)
 };
 
 template <typename T, typename I, bool NUMERIC>
 __device__ __forceinline__ WarpRow<T, I> warp_row_fetch(int64_t idx, int64_t count, int lane, const int32_t* __restrict__ list,
                                                         const T* __restrict__ A_data, const I* __restrict__ A_indices,
                                                         const I* __restrict__ A_indptr, const I* __restrict__ B_indptr) {
-    WarpRow<T, I> w{0, 0, 0, 0, (T)0};
+    WarpRow<T, I> w{0, 0, (I)0, 0, 0};
     if (idx < count) {
         w.row = (int64_t)list[idx];
-        const int64_t a0 = (int64_t)A_indptr[w.row];
-        w.na = (int)((int64_t)A_indptr[w.row + 1] - a0);
+        w.a_begin = (int64_t)A_indptr[w.row];
+        w.na = (int)((int64_t)A_indptr[w.row + 1] - w.a_begin);
         if (lane < w.na) {
-            const int64_t j = (int64_t)A_indices[a0 + lane];
-            w.b_begin = (int64_t)B_indptr[j];
-            w.len = (int)((int64_t)B_indptr[j + 1] - w.b_begin);
-            if (NUMERIC) w.a_val = A_data[a0 + lane];
+            const int64_t j = (int64_t)A_indices[w.a_begin + lane];
+            w.b_begin = B_indptr[j];
+            w.len = (int)((int64_t)B_indptr[j + 1] - (int64_t)w.b_begin);
         }
     }
     return w;
@@ -187,19 +198,26 @@ spgemm_warp_rows_kernel(const int32_t* __restrict__ list, const unsigned long lo
         }
         const int np = __shfl_sync(kAll, incl, 31);
         const bool valid = lane < np;
-        int e = 0;                                     // the entry of A that product `lane` belongs to
-        for (int q = 0; q < cur.na; ++q) e += (__shfl_sync(kAll, incl, q) <= lane);
+        // the entry of A that product `lane` belongs to = the number of entries whose products all come
+        // before it.  When no selected row of B is empty the ends of the runs are distinct, so a bit mask
+        // of them answers that with one population count; otherwise they are compared one by one.
+        int e = 0;
+        const bool in_row = lane < cur.na;
+        if (__all_sync(kAll, !in_row || cur.len > 0)) {
+            const unsigned ends = __reduce_or_sync(kAll, (in_row && incl < 32) ? (1u << incl) : 0u);
+            e = __popc(ends & (0xffffffffu >> (31 - lane)));
+        } else {
+            for (int q = 0; q < cur.na; ++q) e += (__shfl_sync(kAll, incl, q) <= lane);
+        }
         if (!valid) e = 0;
         const int first = __shfl_sync(kAll, incl - cur.len, e);
-        const int64_t b0 = __shfl_sync(kAll, cur.b_begin, e);
-        T a_e = (T)0;
-        if (NUMERIC) a_e = __shfl_sync(kAll, cur.a_val, e);
+        const I b0 = __shfl_sync(kAll, cur.b_begin, e);
         uint32_t c = kEmptyKey;                        // lanes without a product share a column no row has
         T v = (T)0;
         if (valid) {
-            const int64_t b = b0 + (lane - first);
+            const int64_t b = (int64_t)b0 + (lane - first);
             c = (uint32_t)B_indices[b];
-            if (NUMERIC) v = mul_rn(a_e, B_data[b]);
+            if (NUMERIC) v = mul_rn(A_data[cur.a_begin + e], B_data[b]);
         }
         const unsigned group = __match_any_sync(kAll, c);
         const bool leader = valid && lane == __ffs(group) - 1;
@@ -209,13 +227,16 @@ spgemm_warp_rows_kernel(const int32_t* __restrict__ list, const unsigned long lo
         } else {
             int rank = 0;                              // position in the sorted row: leaders with a smaller column
             for (unsigned rem = leaders; rem; rem &= rem - 1) rank += __shfl_sync(kAll, c, __ffs(rem) - 1) < c;
-            // the group's products in lane order = the reference's order of additions
+            // the group's products in lane order = the reference's order of additions (0 + first + ...)
             const int longest = __reduce_max_sync(kAll, valid ? __popc(group) : 0);
-            T sum = (T)0;
-            unsigned rem = group;
-            for (int it = 0; it < longest; ++it) {
-                const T t = __shfl_sync(kAll, v, rem ? __ffs(rem) - 1 : lane);
-                if (rem) { sum = add_rn(sum, t); rem &= rem - 1; }
+            T sum = add_rn((T)0, v);
+            if (longest > 1) {
+                sum = (T)0;
+                unsigned rem = group;
+                for (int it = 0; it < longest; ++it) {
+                    const T t = __shfl_sync(kAll, v, rem ? __ffs(rem) - 1 : lane);
+                    if (rem) { sum = add_rn(sum, t); rem &= rem - 1; }
+                }
             }
             if (leader) {
                 C_indices[c_begin + rank] = (int64_t)c;

@@ -9,6 +9,12 @@
 // output element is bit-identical to a sequential CPU loop.  With `perm` the values are read as
 // data[perm[k]]: the same kernel then computes grad_B = A^T grad_C over a cached transposed
 // structure without atomics.
+//
+// `row_order` (optional): the r-th lane group takes row row_order[r] instead of row r.  With rows
+// sorted by descending length the few very long rows of a skewed matrix (one lane group walks a row
+// alone, 4096 entries take about a millisecond) start first and finish under the cover of the short
+// ones instead of forming a tail; every row is still summed by one group in storage order, so the
+// results do not change by a bit.
 #include "common.cuh"
 
 #ifndef NB200_SPMM_GRAD_BATCH
@@ -51,15 +57,16 @@ __device__ __forceinline__ void store_vec(T* p, const T (&v)[VEC]) {
 template <typename T, typename I, int VEC, int G, bool PERM>
 __global__ void __launch_bounds__(256)
 spdmm_forward_kernel(int64_t rows, int64_t K, const T* __restrict__ data, const I* __restrict__ indices,
-                     const I* __restrict__ indptr, const I* __restrict__ perm,
+                     const I* __restrict__ indptr, const I* __restrict__ perm, const int32_t* __restrict__ row_order,
                      const T* __restrict__ B, T* __restrict__ C) {
     constexpr int ROWS_PER_WARP = 32 / G;
     const int lane = threadIdx.x & 31;
     const int gl = lane % G;                 // lane within the group
     const int gbase = lane - gl;             // first lane of the group (shuffle source offset)
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int64_t r = warp * ROWS_PER_WARP + lane / G;
-    const bool active = r < rows;
+    const int64_t slot = warp * ROWS_PER_WARP + lane / G;
+    const bool active = slot < rows;
+    const int64_t r = (active && row_order) ? (int64_t)row_order[slot] : slot;
     const int64_t s = active ? (int64_t)indptr[r] : 0;
     const int64_t e = active ? (int64_t)indptr[r + 1] : 0;
 
@@ -120,14 +127,16 @@ spdmm_forward_kernel(int64_t rows, int64_t K, const T* __restrict__ data, const 
 template <typename T, typename I, int VEC, int G>
 __global__ void __launch_bounds__(256)
 spdmm_grad_A_kernel(int64_t rows, int64_t K, const I* __restrict__ indices, const I* __restrict__ indptr,
+                    const int32_t* __restrict__ row_order,
                     const T* __restrict__ B, const T* __restrict__ grad_C, T* __restrict__ grad_A) {
     constexpr int ROWS_PER_WARP = 32 / G;
     const int lane = threadIdx.x & 31;
     const int gl = lane % G;
     const int gbase = lane - gl;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int64_t r = warp * ROWS_PER_WARP + lane / G;
-    const bool active = r < rows;
+    const int64_t slot = warp * ROWS_PER_WARP + lane / G;
+    const bool active = slot < rows;
+    const int64_t r = (active && row_order) ? (int64_t)row_order[slot] : slot;
     const int64_t s = active ? (int64_t)indptr[r] : 0;
     const int64_t e = active ? (int64_t)indptr[r + 1] : 0;
     const bool single_tile = K <= (int64_t)G * VEC;
@@ -235,24 +244,24 @@ spdmm_grad_A_kernel(int64_t rows, int64_t K, const I* __restrict__ indices, cons
 
 template <typename T, typename I, int VEC, int G>
 int spdmm_forward_cfg(int64_t rows, int64_t K, const T* data, const I* indices, const I* indptr, const I* perm,
-                      const T* B, T* C, cudaStream_t st) {
+                      const int32_t* row_order, const T* B, T* C, cudaStream_t st) {
     const int64_t warps = ceil_div(rows, (int64_t)(32 / G));
     const int64_t grid = ceil_div(warps, (int64_t)8);
     if (grid > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
     if (perm)
-        spdmm_forward_kernel<T, I, VEC, G, true><<<(unsigned)grid, 256, 0, st>>>(rows, K, data, indices, indptr, perm, B, C);
+        spdmm_forward_kernel<T, I, VEC, G, true><<<(unsigned)grid, 256, 0, st>>>(rows, K, data, indices, indptr, perm, row_order, B, C);
     else
-        spdmm_forward_kernel<T, I, VEC, G, false><<<(unsigned)grid, 256, 0, st>>>(rows, K, data, indices, indptr, perm, B, C);
+        spdmm_forward_kernel<T, I, VEC, G, false><<<(unsigned)grid, 256, 0, st>>>(rows, K, data, indices, indptr, perm, row_order, B, C);
     return launch_status();
 }
 
 template <typename T, typename I, int VEC, int G>
-int spdmm_grad_A_cfg(int64_t rows, int64_t K, const I* indices, const I* indptr, const T* B, const T* grad_C,
-                     T* grad_A, cudaStream_t st) {
+int spdmm_grad_A_cfg(int64_t rows, int64_t K, const I* indices, const I* indptr, const int32_t* row_order,
+                     const T* B, const T* grad_C, T* grad_A, cudaStream_t st) {
     const int64_t warps = ceil_div(rows, (int64_t)(32 / G));
     const int64_t grid = ceil_div(warps, (int64_t)8);
     if (grid > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
-    spdmm_grad_A_kernel<T, I, VEC, G><<<(unsigned)grid, 256, 0, st>>>(rows, K, indices, indptr, B, grad_C, grad_A);
+    spdmm_grad_A_kernel<T, I, VEC, G><<<(unsigned)grid, 256, 0, st>>>(rows, K, indices, indptr, row_order, B, grad_C, grad_A);
     return launch_status();
 }
 
@@ -266,11 +275,11 @@ static inline int pick_group(int64_t K) {
 
 template <typename T, typename I>
 int spdmm_forward_launch(int64_t rows, int64_t K, const T* data, const I* indices, const I* indptr, const I* perm,
-                         const T* B, T* C, cudaStream_t st) {
+                         const int32_t* row_order, const T* B, T* C, cudaStream_t st) {
     if (rows == 0 || K == 0) return NB200_OK;
     constexpr int V = 16 / sizeof(T);
     const bool vec_ok = (K % V == 0) && aligned16(B) && aligned16(C);
-#define NB200_FWD(VEC_, G_) spdmm_forward_cfg<T, I, VEC_, G_>(rows, K, data, indices, indptr, perm, B, C, st)
+#define NB200_FWD(VEC_, G_) spdmm_forward_cfg<T, I, VEC_, G_>(rows, K, data, indices, indptr, perm, row_order, B, C, st)
     if (vec_ok) {
         switch (pick_group<V>(K)) {
             case 8: return NB200_FWD(V, 8);
@@ -287,12 +296,12 @@ int spdmm_forward_launch(int64_t rows, int64_t K, const T* data, const I* indice
 }
 
 template <typename T, typename I>
-int spdmm_grad_A_launch(int64_t rows, int64_t K, const I* indices, const I* indptr, const T* B, const T* grad_C,
-                        T* grad_A, cudaStream_t st) {
+int spdmm_grad_A_launch(int64_t rows, int64_t K, const I* indices, const I* indptr, const int32_t* row_order,
+                        const T* B, const T* grad_C, T* grad_A, cudaStream_t st) {
     if (rows == 0) return NB200_OK;
     constexpr int V = 16 / sizeof(T);
     const bool vec_ok = (K % V == 0) && aligned16(B) && aligned16(grad_C) && K > 0;
-#define NB200_GA(VEC_, G_) spdmm_grad_A_cfg<T, I, VEC_, G_>(rows, K, indices, indptr, B, grad_C, grad_A, st)
+#define NB200_GA(VEC_, G_) spdmm_grad_A_cfg<T, I, VEC_, G_>(rows, K, indices, indptr, row_order, B, grad_C, grad_A, st)
     if (vec_ok) {
         switch (pick_group<V>(K)) {
             case 8: return NB200_GA(V, 8);
@@ -314,7 +323,8 @@ using namespace nb200;
 
 extern "C" int nb200_spdmm_forward(int64_t rows, int64_t cols, int64_t K, int64_t nnz,
                                    const void* data, const void* indices, const void* indptr, const void* perm,
-                                   const void* B, void* C, int dtype, int itype, nb200_stream stream) {
+                                   const int32_t* row_order, const void* B, void* C, int dtype, int itype,
+                                   nb200_stream stream) {
     (void)cols;
     if (rows < 0 || cols < 0 || K < 0 || nnz < 0) return NB200_ERR_BAD_ARG;
     if (rows == 0 || K == 0) return NB200_OK;
@@ -322,11 +332,11 @@ extern "C" int nb200_spdmm_forward(int64_t rows, int64_t cols, int64_t K, int64_
     if (itype == NB200_I32 && nnz > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
     return NB200_DISPATCH(dtype, itype,
         (spdmm_forward_launch<T, I>(rows, K, (const T*)data, (const I*)indices, (const I*)indptr, (const I*)perm,
-                                    (const T*)B, (T*)C, as_stream(stream))));
+                                    row_order, (const T*)B, (T*)C, as_stream(stream))));
 }
 
 extern "C" int nb200_spdmm_backward_grad_A(int64_t rows, int64_t cols, int64_t K, int64_t nnz,
-                                           const void* indices, const void* indptr,
+                                           const void* indices, const void* indptr, const int32_t* row_order,
                                            const void* B, const void* grad_C, void* grad_A,
                                            int dtype, int itype, nb200_stream stream) {
     (void)cols;
@@ -335,6 +345,6 @@ extern "C" int nb200_spdmm_backward_grad_A(int64_t rows, int64_t cols, int64_t K
     if (!indptr || !indices || !grad_A || (K > 0 && (!B || !grad_C))) return NB200_ERR_BAD_ARG;
     if (itype == NB200_I32 && nnz > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
     return NB200_DISPATCH(dtype, itype,
-        (spdmm_grad_A_launch<T, I>(rows, K, (const I*)indices, (const I*)indptr, (const T*)B, (const T*)grad_C,
-                                   (T*)grad_A, as_stream(stream))));
+        (spdmm_grad_A_launch<T, I>(rows, K, (const I*)indices, (const I*)indptr, row_order, (const T*)B,
+                                   (const T*)grad_C, (T*)grad_A, as_stream(stream))));
 }

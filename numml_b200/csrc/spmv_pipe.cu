@@ -97,11 +97,12 @@ struct PipeArgs {
 // transposed value of GATHER entries at a time with asynchronous copies into shared-memory slots of
 // its own instead of into registers.  All gathers of a short row are then in flight at once and a
 // block costs one memory round trip, where the register version needs one per CH entries.
-template <typename T, typename I, int MODE, int S, bool DIRECT = false, int GATHER = 0>
+template <typename T, typename I, int MODE, int S, bool DIRECT = false, int GATHER = 0, int WSTORE = 0>
 struct PipeSmem {
     static constexpr bool has_a = MODE != kGradA;
     static constexpr bool a_is_perm = MODE == kForwardPerm || MODE == kBackwardSym;
-    static constexpr bool has_p = (MODE == kGradA || is_backward_sym(MODE)) && !DIRECT;
+    // grad_A is staged per block (!DIRECT), or per warp when the stage has no value slots to reuse
+    static constexpr bool has_p = ((MODE == kGradA || is_backward_sym(MODE)) && !DIRECT) || (MODE == kBackwardSym && WSTORE != 0);
     static constexpr size_t a_bytes = has_a ? (a_is_perm ? sizeof(I) : sizeof(T)) * kPipeTile : 0;  // values | perm
     static constexpr size_t b_bytes = sizeof(I) * kPipeTile;                                           // indices
     static constexpr size_t p_bytes = has_p ? sizeof(T) * kPipeTile : 0;                               // grad_A staging
@@ -158,10 +159,18 @@ __device__ __forceinline__ void sts4<double>(double* p, const double (&v)[4]) {
     *reinterpret_cast<double2*>(p + 2) = make_double2(v[2], v[3]);
 }
 
-template <typename T, typename I, int MODE, int S, int CH, int MINB, bool DIRECT, int GATHER>
+// WSTORE (fused backward with direct stores): where a row thread puts its grad_A entries.
+//   0  straight to global memory, one or two entries per store (a warp's store touches 32 sectors)
+//   1  into shared memory -- the stage's value slots, which the thread has just consumed (kBackwardSymVal), or
+//      a staging area of the stage (kBackwardSym); the warp's rows are contiguous in grad_A, so after a warp
+//      barrier the lanes copy the warp's range out with 16-byte stores, fully coalesced
+//   2  the same, but the copy-out is one bulk shared-to-global copy issued by one lane (TMA store)
+template <typename T, typename I, int MODE, int S, int CH, int MINB, bool DIRECT, int GATHER, int WSTORE>
 __global__ void __launch_bounds__(kPipeThreads, MINB)
 spmv_pipe_kernel(const PipeArgs<T, I> a) {
-    using L = PipeSmem<T, I, MODE, S, DIRECT, GATHER>;
+    static_assert(WSTORE == 0 || (DIRECT && ((MODE == kBackwardSymVal && GATHER == 0) || (MODE == kBackwardSym && GATHER > 0))),
+                  "per-warp staging of grad_A: in the consumed value slots, or in an area of its own");
+    using L = PipeSmem<T, I, MODE, S, DIRECT, GATHER, WSTORE>;
     constexpr int kPipeStages = S;
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -306,9 +315,12 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
                         if (!kStagedValues) async_copy_elem(sd + e * kPipeConsumers, a.data + sperm[o0 + e]);
                     }
                     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
-                    // (2) grad_A[k] = g_i x_c, two entries per vector store where the address allows
+                    // (2) grad_A[k] = g_i x_c, staged for the warp's copy-out or stored two entries at a time
                     int e = 0;
-                    if (o0 & 1) { outp[o0] = mul_rn(gi, sx[0]); e = 1; }
+                    if (WSTORE != 0) {
+                        for (; e < n; ++e) sout[o0 + e] = mul_rn(gi, sx[e * kPipeConsumers]);
+                    }
+                    if (e < n && (o0 & 1)) { outp[o0] = mul_rn(gi, sx[0]); e = 1; }
                     for (; e + 2 <= n; e += 2) {
                         T2 w;
                         w.x = mul_rn(gi, sx[e * kPipeConsumers]);
@@ -367,7 +379,9 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
                         if (j < n) {
                             const int o = o0 + j;
                             const T val = mul_rn(cur.g, xv[j]);
-                            if (!DIRECT && o < kPipeTile) sout[o] = val; else outp[o] = val;
+                            if (WSTORE != 0 && o < staged_cnt) const_cast<T*>(sval)[o] = val;   // slot o was read into v[j] above
+                            else if (!DIRECT && o < kPipeTile) sout[o] = val;
+                            else outp[o] = val;
                             acc = add_rn(acc, mul_rn(gv[j], v[j]));
                         }
                     }
@@ -388,6 +402,32 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
             }
             if (MODE == kForward || MODE == kForwardPerm) a.out[r0 + tid] = acc;
             if (is_backward_sym(MODE)) a.out2[r0 + tid] = acc;
+        }
+        if (WSTORE != 0 && stage_ready) {
+            // ---- the warp's grad_A entries leave the stage as whole lines ----
+            constexpr int V = 16 / (int)sizeof(T);                       // entries per 16 bytes
+            const int lane = tid & 31;
+            const int lo_w = __reduce_min_sync(0xffffffffu, owns_row ? cur.lo + shift : 0x7fffffff);
+            const int hi_w = __reduce_max_sync(0xffffffffu, owns_row ? min(cur.hi + shift, staged_cnt) : 0);
+            T* const sstage = MODE == kBackwardSymVal ? const_cast<T*>(sval) : sout;
+            if (WSTORE == 2) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (hi_w > lo_w) {
+                const int lo_a = min((lo_w + V - 1) & ~(V - 1), hi_w);   // outp + o is 16-byte aligned when o % V == 0
+                const int hi_a = max(hi_w & ~(V - 1), lo_a);
+                if (lane < lo_a - lo_w) outp[lo_w + lane] = sstage[lo_w + lane];
+                if (lane < hi_w - hi_a) outp[hi_a + lane] = sstage[hi_a + lane];
+                if (WSTORE == 2) {
+                    if (lane == 0 && hi_a > lo_a) {
+                        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                     :: "l"(outp + lo_a), "r"(smem_u32(sstage + lo_a)), "r"((unsigned)((hi_a - lo_a) * sizeof(T))) : "memory");
+                        asm volatile("cp.async.bulk.commit_group;\n\tcp.async.bulk.wait_group.read 0;" ::: "memory");
+                    }
+                } else {
+                    for (int o = lo_a + V * lane; o < hi_a; o += 32 * V)
+                        *reinterpret_cast<int4*>(outp + o) = *reinterpret_cast<const int4*>(sstage + o);
+                }
+            }
         }
         if ((MODE == kGradA || is_backward_sym(MODE)) && !DIRECT) {
             // ---- coalesced 128-bit stores of the block's grad_A entries ----
@@ -418,12 +458,12 @@ spmv_pipe_kernel(const PipeArgs<T, I> a) {
     }
 }
 
-template <typename T, typename I, int MODE, int S, int CH = 8, int MINB = 3, bool DIRECT = false, int GATHER = 0>
+template <typename T, typename I, int MODE, int S, int CH = 8, int MINB = 3, bool DIRECT = false, int GATHER = 0, int WSTORE = 0>
 int spmv_pipe_launch(const PipeArgs<T, I>& args, cudaStream_t st) {
-    using L = PipeSmem<T, I, MODE, S, DIRECT, GATHER>;
+    using L = PipeSmem<T, I, MODE, S, DIRECT, GATHER, WSTORE>;
     // the opt-in to more than 48 KB of dynamic shared memory is a per-device property of the kernel
     static std::atomic<bool> configured[kMaxDevices];
-    auto kernel = spmv_pipe_kernel<T, I, MODE, S, CH, MINB, DIRECT, GATHER>;
+    auto kernel = spmv_pipe_kernel<T, I, MODE, S, CH, MINB, DIRECT, GATHER, WSTORE>;
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return NB200_ERR_CUDA;
     if (!configured[device].load(std::memory_order_acquire)) {
@@ -457,8 +497,18 @@ int spmv_pipe_grad_A(int64_t rows, int64_t nnz, int block_rows, const I* indices
     return spmv_pipe_launch<T, I, kGradA, 2, 4, 4>(a, st);
 }
 
-#ifndef NB200_SYMVAL_VARIANT
-#define NB200_SYMVAL_VARIANT 0
+// Configuration of the two fused backward kernels, overridable for tuning builds.
+#ifndef NB200_SYMVAL_CH
+#define NB200_SYMVAL_CH 4          // entries per gather round
+#endif
+#ifndef NB200_SYMVAL_MINB
+#define NB200_SYMVAL_MINB 4        // CTAs per SM
+#endif
+#ifndef NB200_SYMVAL_WSTORE
+#define NB200_SYMVAL_WSTORE 2      // grad_A leaves through the consumed value slots as a bulk copy per warp
+#endif
+#ifndef NB200_SYM_WSTORE
+#define NB200_SYM_WSTORE 0
 #endif
 
 template <typename T, typename I>
@@ -468,21 +518,13 @@ int spmv_pipe_backward_sym(int64_t row_begin, int64_t row_end, int64_t nnz, int 
     if (row_end <= row_begin) return NB200_OK;
     PipeArgs<T, I> a{row_begin, row_end, nnz, ceil_div(row_end - row_begin, (int64_t)block_rows), block_rows, data, indices, indptr, perm, x, g, grad_A, grad_x, status};
     if (values_symmetric) {
-        // values and indices staged by bulk copies, x_c and g_c gathered: the traffic is exactly the
-        // credited bytes of the backward (no permutation, no value gather)
-#if NB200_SYMVAL_VARIANT == 0
-        return spmv_pipe_launch<T, I, kBackwardSymVal, 2, 4, 4, true, 0>(a, st);
-#elif NB200_SYMVAL_VARIANT == 1
-        return spmv_pipe_launch<T, I, kBackwardSymVal, 2, 2, 4, true, 0>(a, st);
-#elif NB200_SYMVAL_VARIANT == 2
-        return spmv_pipe_launch<T, I, kBackwardSymVal, 2, 2, 2, true, 8>(a, st);
-#elif NB200_SYMVAL_VARIANT == 3
-        return spmv_pipe_launch<T, I, kBackwardSymVal, 2, 2, 3, true, 4>(a, st);
-#elif NB200_SYMVAL_VARIANT == 4
-        return spmv_pipe_launch<T, I, kBackwardSymVal, 2, 8, 3, true, 0>(a, st);
-#else
-        return spmv_pipe_launch<T, I, kBackwardSymVal, 3, 4, 3, true, 0>(a, st);
-#endif
+        // Values and indices staged by bulk copies, x_c and g_c gathered into registers: the traffic is
+        // exactly the credited bytes of the backward (no permutation, no value gather).  Measured on the
+        // 128^3 Poisson matrix (us), 2 stages: grad_A stored entry by entry from the row threads, 4 entries
+        // per round / 4 CTAs per SM 79.7, 8 / 3 83.4; staged in the consumed value slots and copied out by
+        // the warp with 16-byte stores 67.3 (2 entries per round 65.6; 3 stages / 3 CTAs 68.6); copied out
+        // by one bulk shared-to-global copy per warp 63.6 (8 / 3: 79.6; 3 stages / 3 CTAs 66.8).
+        return spmv_pipe_launch<T, I, kBackwardSymVal, 2, NB200_SYMVAL_CH, NB200_SYMVAL_MINB, true, 0, NB200_SYMVAL_WSTORE>(a, st);
     }
     // Measured on the 128^3 Poisson matrix (us).  Gathers into registers, grad_A written straight from the
     // row threads: 2 stages / 2 entries per round / 4 CTAs per SM 94.5; 2/4/4 98; 4/4/3 104; 3/8/3 112; 5+ CTAs
@@ -491,7 +533,7 @@ int spmv_pipe_backward_sym(int64_t row_begin, int64_t row_end, int64_t nnz, int 
     // (7 or 6 slots) 133 -- the L1 that the gathers land in shrinks to a few KB; x through registers 88-98; a
     // single stage 97-128; staging the block's own slice of `data` 95; staging grad_A over the dead index
     // area 101; fetching the transposed value as an L1-bypassing 16-byte group 103.
-    return spmv_pipe_launch<T, I, kBackwardSym, 2, 2, 2, true, 8>(a, st);
+    return spmv_pipe_launch<T, I, kBackwardSym, 2, 2, 2, true, 8, NB200_SYM_WSTORE>(a, st);
 }
 
 #define NB200_INSTANTIATE_PIPE(T, I)                                                                                 \

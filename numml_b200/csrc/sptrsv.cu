@@ -1,10 +1,12 @@
 // Sparse triangular solve (forward and the pieces of its backward) for CSR on sm_100a.
 //
-// Analysis (once per sparsity pattern and triangle): dependency levels by frontier peeling
-// (Kahn): a row is ready when every strictly-triangular entry of it refers to a solved row.
-// One small kernel per level walks the current frontier through the transposed structure and
-// decrements the in-degree of the dependents; no kernel ever waits on another.  Rows are then
-// sorted by (level, row) into `order`.
+// Analysis (once per sparsity pattern and triangle): the dependency level of a row is one more than
+// the largest level among the rows its strictly-triangular entries refer to (0 without any).  One
+// launch computes all of them with the scheme the solve uses: one thread per row, rows taken in
+// dependency order (ascending for a lower triangle, descending for an upper one), the level array
+// pre-filled with -1 and polled as its own ready flag, a thread publishing its level from inside its
+// poll loop so that lanes of one warp can depend on one another.  Polls are bounded by a cycle
+// budget.  Rows are then sorted by (level, row) into `order`.
 //
 // Solve: one launch.  Row order[p] is owned by the p-th team (a team is as many lanes as there
 // are right-hand sides, up to 32, so a dependency x[j, :] is read as one contiguous line).
@@ -28,47 +30,48 @@ namespace nb200 {
 // ---------------------------------------------------------------------------------------------
 // Analysis kernels
 // ---------------------------------------------------------------------------------------------
-// counters: [0..2] rotating frontier sizes, [3] rows finished, [4] number of levels, [5] done flag
-template <typename I>
-__global__ void sptrsv_indegree_kernel(int64_t n, const I* __restrict__ indices, const I* __restrict__ indptr,
-                                       bool lower, int32_t* __restrict__ indeg, int32_t* __restrict__ frontier,
-                                       int32_t* __restrict__ counters) {
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        int32_t deps = 0;
-        for (int64_t k = (int64_t)indptr[i]; k < (int64_t)indptr[i + 1]; ++k) {
-            const int64_t j = (int64_t)indices[k];
-            deps += lower ? (j < i) : (j > i);
-        }
-        indeg[i] = deps;
-        if (deps == 0) frontier[atomicAdd(counters + 0, 1)] = (int32_t)i;
-    }
+__device__ __forceinline__ int ld_relaxed_level(const int32_t* p) {
+    int v;
+    asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_level(int32_t* p, int v) {
+    asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
 }
 
+// counters: [0] number of levels (largest level + 1), [1] non-zero if a wait ran out
 template <typename I>
-__global__ void sptrsv_kahn_kernel(int32_t level, bool lower, const I* __restrict__ t_indptr,
-                                   const I* __restrict__ t_indices, const int32_t* __restrict__ frontier_in,
-                                   int32_t* __restrict__ frontier_out, int32_t* __restrict__ indeg,
-                                   uint32_t* __restrict__ level_of, int32_t* __restrict__ counters) {
-    const int32_t n_in = counters[level % 3];
-    int32_t* n_out = counters + (level + 1) % 3;
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-        counters[(level + 2) % 3] = 0;   // next kernel's output counter
-        if (n_in == 0) {
-            if (counters[5] == 0) { counters[4] = level; counters[5] = 1; }
-        } else {
-            counters[3] += n_in;
-        }
-    }
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; f < n_in; f += stride) {
-        const int64_t j = frontier_in[f];
-        level_of[j] = (uint32_t)level;
-        for (int64_t a = (int64_t)t_indptr[j]; a < (int64_t)t_indptr[j + 1]; ++a) {
-            const int64_t i = (int64_t)t_indices[a];     // entry (i, j) of the matrix
-            if (lower ? (i > j) : (i < j)) {
-                if (atomicSub(indeg + i, 1) == 1) frontier_out[atomicAdd(n_out, 1)] = (int32_t)i;
+__global__ void __launch_bounds__(256)
+sptrsv_levels_kernel(int64_t n, const I* __restrict__ indices, const I* __restrict__ indptr, bool lower,
+                     int32_t* __restrict__ level, int32_t* __restrict__ counters, long long budget) {
+    const int64_t pos = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (pos >= n) return;
+    // dependencies of row i lie before it in this order, i.e. with threads that were dispatched earlier
+    const int64_t i = lower ? pos : n - 1 - pos;
+    int64_t k = (int64_t)indptr[i];
+    const int64_t end = (int64_t)indptr[i + 1];
+    int lvl = 0;
+    long long t0 = 0;
+    for (unsigned spins = 0;; ++spins) {
+        while (k < end) {                                   // as far as the known levels reach
+            const int64_t j = (int64_t)indices[k];
+            if (lower ? (j < i) : (j > i)) {
+                const int v = ld_relaxed_level(level + j);
+                if (v < 0) break;
+                lvl = max(lvl, v + 1);
             }
+            ++k;
+        }
+        if (k >= end) {                                     // published from inside the loop: a lane of the
+            st_relaxed_level(level + i, lvl);               // same warp that waits for this row sees it on
+            atomicMax(counters + 0, lvl + 1);               // its next round, wherever the warp reconverges
+            break;
+        }
+        if (spins == 0) t0 = clock64();
+        if ((spins & 63u) == 63u && (ld_relaxed_level(counters + 1) != 0 || clock64() - t0 > budget)) {
+            atomicExch(counters + 1, 1);
+            st_relaxed_level(level + i, 0);                 // let the waiters go; the caller sees the flag
+            break;
         }
     }
 }
@@ -220,19 +223,17 @@ static inline int bit_length(int64_t v) {
 
 static size_t analysis_workspace_bytes(int64_t n) {
     const size_t m = (size_t)(n > 0 ? n : 1);
-    // indeg, two frontiers, level keys a/b, row ids a/b, counters, sort scratch
-    return 7 * Workspace::pad(m * sizeof(int32_t)) + Workspace::pad(8 * sizeof(int32_t)) + Workspace::pad(sort_scratch_bytes(n));
+    // level keys a/b, row ids a/b, counters, sort scratch
+    return 4 * Workspace::pad(m * sizeof(int32_t)) + Workspace::pad(8 * sizeof(int32_t)) + Workspace::pad(sort_scratch_bytes(n));
 }
 
 template <typename I>
-int sptrsv_analyse(int64_t n, const I* indices, const I* indptr, const I* t_indptr, const I* t_indices, bool lower,
+int sptrsv_analyse(int64_t n, const I* indices, const I* indptr, bool lower,
                    int32_t* order, int64_t* nlevels_host, void* workspace, size_t bytes, cudaStream_t st) {
     *nlevels_host = 0;
     if (n == 0) return NB200_OK;
     const size_t m = (size_t)n;
     Workspace ws(workspace, bytes);
-    int32_t* indeg = ws.take<int32_t>(m);
-    int32_t* front[2] = {ws.take<int32_t>(m), ws.take<int32_t>(m)};
     uint32_t* key_a = ws.take<uint32_t>(m);
     uint32_t* key_b = ws.take<uint32_t>(m);
     uint32_t* val_a = ws.take<uint32_t>(m);
@@ -243,26 +244,16 @@ int sptrsv_analyse(int64_t n, const I* indices, const I* indptr, const I* t_indp
     if (!ws.ok()) return NB200_ERR_WORKSPACE;
 
     if (cudaMemsetAsync(counters, 0, 8 * sizeof(int32_t), st) != cudaSuccess) return NB200_ERR_CUDA;
-    // rows that are never reached (cannot happen for a triangular dependency graph) keep level 0
-    if (cudaMemsetAsync(key_a, 0, m * sizeof(uint32_t), st) != cudaSuccess) return NB200_ERR_CUDA;
-    sptrsv_indegree_kernel<I><<<flat_grid(n), 256, 0, st>>>(n, indices, indptr, lower, indeg, front[0], counters);
-
-    const unsigned kgrid = (unsigned)(kSMs * 2);
+    if (cudaMemsetAsync(key_a, 0xff, m * sizeof(uint32_t), st) != cudaSuccess) return NB200_ERR_CUDA;   // -1: level unknown
+    const int64_t grid = ceil_div(n, (int64_t)256);
+    sptrsv_levels_kernel<I><<<(unsigned)grid, 256, 0, st>>>(n, indices, indptr, lower, reinterpret_cast<int32_t*>(key_a),
+                                                           counters, 4000000000LL);
     int32_t host_counters[8] = {0};
-    int32_t level = 0;
-    const int32_t chunk = 128;
-    while (true) {
-        for (int32_t q = 0; q < chunk; ++q, ++level)
-            sptrsv_kahn_kernel<I><<<kgrid, 256, 0, st>>>(level, lower, t_indptr, t_indices, front[level & 1],
-                                                       front[(level + 1) & 1], indeg, key_a, counters);
-        if (cudaMemcpyAsync(host_counters, counters, sizeof(host_counters), cudaMemcpyDeviceToHost, st) != cudaSuccess)
-            return NB200_ERR_CUDA;
-        if (cudaStreamSynchronize(st) != cudaSuccess) return NB200_ERR_CUDA;
-        if (host_counters[5] != 0) break;
-        if ((int64_t)level > n + chunk) return NB200_ERR_PRECONDITION;   // cannot need more levels than rows
-    }
-    if ((int64_t)host_counters[3] != n) return NB200_ERR_PRECONDITION;
-    const int64_t nlevels = host_counters[4];
+    if (cudaMemcpyAsync(host_counters, counters, sizeof(host_counters), cudaMemcpyDeviceToHost, st) != cudaSuccess)
+        return NB200_ERR_CUDA;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return NB200_ERR_CUDA;
+    if (host_counters[1] != 0) return NB200_ERR_WAIT_BUDGET;
+    const int64_t nlevels = host_counters[0];
     *nlevels_host = nlevels;
 
     sptrsv_iota_kernel<<<flat_grid(n), 256, 0, st>>>(n, val_a);
@@ -308,10 +299,10 @@ extern "C" int nb200_sptrsv_analyse(int64_t n, int64_t nnz, const void* indices,
                                     void* workspace, size_t workspace_bytes, nb200_stream stream) {
     if (n < 0 || nnz < 0 || !nlevels_host) return NB200_ERR_BAD_ARG;
     if (n >= 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
-    if (n > 0 && (!indptr || !t_indptr || !order || !workspace || (nnz > 0 && (!indices || !t_indices))))
-        return NB200_ERR_BAD_ARG;
+    (void)t_indptr; (void)t_indices;
+    if (n > 0 && (!indptr || !order || !workspace || (nnz > 0 && !indices))) return NB200_ERR_BAD_ARG;
     return NB200_DISPATCH_I(itype,
-        (sptrsv_analyse<I>(n, (const I*)indices, (const I*)indptr, (const I*)t_indptr, (const I*)t_indices, lower != 0,
+        (sptrsv_analyse<I>(n, (const I*)indices, (const I*)indptr, lower != 0,
                            order, nlevels_host, workspace, workspace_bytes, as_stream(stream))));
 }
 

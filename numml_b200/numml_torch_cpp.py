@@ -199,8 +199,9 @@ def spdmm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B):
     K = int(B.shape[1])
     with _on(dev):
         C = torch.empty((A_rows, K), dtype=A_data.dtype, device=dev)
+        order = plan.spmm_row_order()
         _cabi.call("nb200_spdmm_forward", A_rows, A_cols, K, plan.nnz, _ptr(A_data), _ptr(idx), _ptr(ptr), None,
-                   _ptr(B), _ptr(C), _dtype_code(A_data), itype, _stream())
+                   _ptr(order) if order is not None else None, _ptr(B), _ptr(C), _dtype_code(A_data), itype, _stream())
     return C
 
 
@@ -217,11 +218,12 @@ def spdmm_backward(A_rows, A_cols, A_data, A_indices, A_indptr, B, grad_C):
     with _on(dev):
         grad_A = torch.empty_like(A_data)
         grad_B = torch.empty((A_cols, K), dtype=A_data.dtype, device=dev)
+        order, t_order = plan.spmm_row_order(), plan.spmm_row_order(transposed=True)
         _cabi.call("nb200_spdmm_backward_grad_A", A_rows, A_cols, K, plan.nnz, _ptr(idx), _ptr(ptr),
-                   _ptr(B), _ptr(G), _ptr(grad_A), code, itype, _stream())
+                   _ptr(order) if order is not None else None, _ptr(B), _ptr(G), _ptr(grad_A), code, itype, _stream())
         # grad_B = A^T grad_C: the forward kernel over the transposed structure, values via the permutation
         _cabi.call("nb200_spdmm_forward", A_cols, A_rows, K, plan.nnz, _ptr(A_data), _ptr(t_indices), _ptr(t_indptr),
-                   _ptr(t_perm), _ptr(G), _ptr(grad_B), code, itype, _stream())
+                   _ptr(t_perm), _ptr(t_order) if t_order is not None else None, _ptr(G), _ptr(grad_B), code, itype, _stream())
     return [grad_A, grad_B]
 
 

@@ -249,8 +249,9 @@ def test_c3_powerlaw_spmm_full_size(oracle, ops):
     assert_same(Y_ref, Y[sample.cuda()], "rows of Y")
     gA_ref, _ = oracle.spdmm_backward(sample.numel(), cols.numel(), sub_d, sub_idx, sub_ptr, Xs, Gs)
     assert_close(gA_ref, gA[pos.cuda()], "grad_A entries of the sampled rows")
-    worst = float(torch.max(torch.abs(gA_ref - gA[pos.cuda()].cpu()) / (torch.abs(gA_ref) + 1e-3)))
-    assert worst < 1e-3, worst
+    # entry by entry: each is a dot product of 128 terms of size ~1 reduced across lanes in another order
+    worst = float(torch.max(torch.abs(gA_ref - gA[pos.cuda()].cpu())))
+    assert worst < 1e-4, worst
 
     # grad_X = A^T G for a sample of columns: the entries of those columns from a transposed copy
     import scipy.sparse as sps
