@@ -568,7 +568,9 @@ def multi_gpu_spmv(n, ctx, ops, nz_total=None):
 
     info = {"nnz": int(d.numel()), "rows": rows, "cols": engine.n_ext, "status_word": engine.status, "schedule": mode,
             "kernels": ("tma-pipelined, fused backward over ghost rows" if engine.fused else "tma-pipelined") if engine.br else "register-staged",
-            "backward": "spmv_pipe_kernel mode 3 over the ghost-row extension" if engine.fused else "grad_A pass + transposed pass",
+            "backward": ("spmv_pipe_kernel over the ghost-row extension: local rows mode "
+                         + ("4 (pattern and values symmetric)" if engine.values_symmetric else "3 (symmetric pattern)")
+                         + ", ghost rows mode 3") if engine.fused else "grad_A pass + transposed pass",
             "launches_formula": engine.launches_per_step, "exchange": engine.exchange,
             "h2d_bytes": 2 * rows * 8, "d2h_bytes": (2 * rows + int(d.numel())) * 8, "roofline": None, "verify": verify,
             "engine": engine}

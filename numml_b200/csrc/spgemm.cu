@@ -9,8 +9,9 @@
 //             each other with match.any, the lowest lane of a group is its leader, a leader's position in
 //             the sorted row is the number of leaders with a smaller column, and the group's products are
 //             added in lane order -- the reference's order, so these rows come out bit-identical to its
-//             CPU loop and the same from run to run.  The next row's index chain (row of A, row pointers
-//             of B) is fetched while the current row's products are formed.
+//             CPU loop and the same from run to run.  The loads behind a row form a chain five levels deep;
+//             a warp keeps five rows in flight, one per level, so that the chain's latency is paid once per
+//             five rows.
 // The other bins have a team size and an open-addressing hash table:
 //     bin 1:   8 lanes per row,  64-slot table in shared memory      (size <= 32)
 //     bin 2:  32 lanes per row, 512-slot table in shared memory      (size <= 256)
@@ -144,35 +145,14 @@ spgemm_classify_kernel(int64_t rows, const int32_t* __restrict__ size_in,
 // ---------------------------------------------------------------------------------------------
 // Bin 0: one warp per row, no table.
 // ---------------------------------------------------------------------------------------------
-template <typename T, typename I>
-struct WarpRow {          // what the lanes hold about a row before its products are formed
-    int64_t row;
-    int64_t a_begin;      // position of the row's first entry in A
-    I b_begin;            // lane e < na: first position of the row of B that entry e of the row of A selects
-    int len;              // lane e < na: length of that row of B
-    int na;               // entries of the row of A
-};
+// The kernel is bound by the chain of dependent loads behind every row (row list -> row pointers of A
+// -> entries of A -> row pointers of B -> entries of B), not by arithmetic, so the chain is software-
+// pipelined five rows deep: in every iteration a warp issues one load level for each of the five rows
+// it has in flight and only then forms the row whose products arrived during the previous iteration.
+constexpr int kWarpRowsCtasPerSm = 5;      // 48 registers per thread: five 256-thread CTAs fit an SM
 
 template <typename T, typename I, bool NUMERIC>
-__device__ __forceinline__ WarpRow<T, I> warp_row_fetch(int64_t idx, int64_t count, int lane, const int32_t* __restrict__ list,
-                                                        const T* __restrict__ A_data, const I* __restrict__ A_indices,
-                                                        const I* __restrict__ A_indptr, const I* __restrict__ B_indptr) {
-    WarpRow<T, I> w{0, 0, (I)0, 0, 0};
-    if (idx < count) {
-        w.row = (int64_t)list[idx];
-        w.a_begin = (int64_t)A_indptr[w.row];
-        w.na = (int)((int64_t)A_indptr[w.row + 1] - w.a_begin);
-        if (lane < w.na) {
-            const int64_t j = (int64_t)A_indices[w.a_begin + lane];
-            w.b_begin = B_indptr[j];
-            w.len = (int)((int64_t)B_indptr[j + 1] - (int64_t)w.b_begin);
-        }
-    }
-    return w;
-}
-
-template <typename T, typename I, bool NUMERIC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, kWarpRowsCtasPerSm)
 spgemm_warp_rows_kernel(const int32_t* __restrict__ list, const unsigned long long* __restrict__ count_ptr,
                         const T* __restrict__ A_data, const I* __restrict__ A_indices, const I* __restrict__ A_indptr,
                         const T* __restrict__ B_data, const I* __restrict__ B_indices, const I* __restrict__ B_indptr,
@@ -182,68 +162,100 @@ spgemm_warp_rows_kernel(const int32_t* __restrict__ list, const unsigned long lo
     const int lane = threadIdx.x & 31;
     const int64_t count = (int64_t)*count_ptr;
     const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
-    int64_t idx = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    WarpRow<T, I> cur = warp_row_fetch<T, I, NUMERIC>(idx, count, lane, list, A_data, A_indices, A_indptr, B_indptr);
-    for (; idx < count; idx += nwarps) {
-        // the next row's index chain is in flight while this row's products are formed
-        const WarpRow<T, I> nxt = warp_row_fetch<T, I, NUMERIC>(idx + nwarps, count, lane, list, A_data, A_indices, A_indptr, B_indptr);
-        int64_t c_begin = 0;
-        if (NUMERIC) c_begin = C_indptr[cur.row];
-        // products of entry e occupy lanes [incl_e - len_e, incl_e)
-        int incl = cur.len;
+    const int64_t first_idx = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    // stage registers; a row of -1 marks an empty pipeline slot (warp-uniform)
+    int64_t row1 = -1;                                            // 1: row number
+    int64_t row2 = -1, a2 = 0; int na2 = 0;                       // 2: its range in A
+    int64_t row3 = -1, a3 = 0; int na3 = 0; int64_t j3 = 0;       // 3: lane e < na: the row of B that entry e selects
+    int64_t row4 = -1, a4 = 0; int na4 = 0; I bb4 = 0; int len4 = 0;   // 4: lane e < na: that row's range in B
+    int64_t row5 = -1, cbeg5 = 0; uint32_t c5 = kEmptyKey; T v5 = (T)0; bool valid5 = false;   // 5: lane p: product p
+    for (int64_t idx = first_idx; idx < count + 5 * nwarps; idx += nwarps) {
+        // ---- level 5 for the row in slot 4: place the products on the lanes and request them ----
+        int64_t n_row5 = row4, n_cbeg5 = 0;
+        uint32_t n_c5 = kEmptyKey;
+        T n_v5 = (T)0;
+        bool n_valid5 = false;
+        if (row4 >= 0) {
+            // products of entry e occupy lanes [incl_e - len_e, incl_e)
+            int incl = len4;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(kAll, incl, o);
-            if (lane >= o) incl += t;
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(kAll, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const int np = __shfl_sync(kAll, incl, 31);
+            n_valid5 = lane < np;
+            // the entry of A that product `lane` belongs to = the number of entries whose products all come
+            // before it.  When no selected row of B is empty the ends of the runs are distinct, so a bit mask
+            // of them answers that with one population count; otherwise they are compared one by one.
+            int e = 0;
+            const bool in_row = lane < na4;
+            if (__all_sync(kAll, !in_row || len4 > 0)) {
+                const unsigned ends = __reduce_or_sync(kAll, (in_row && incl < 32) ? (1u << incl) : 0u);
+                e = __popc(ends & (0xffffffffu >> (31 - lane)));
+            } else {
+                for (int q = 0; q < na4; ++q) e += (__shfl_sync(kAll, incl, q) <= lane);
+            }
+            if (!n_valid5) e = 0;
+            const int first = __shfl_sync(kAll, incl - len4, e);
+            const I b0 = __shfl_sync(kAll, bb4, e);
+            if (n_valid5) {
+                const int64_t b = (int64_t)b0 + (lane - first);
+                n_c5 = (uint32_t)B_indices[b];
+                if (NUMERIC) n_v5 = mul_rn(A_data[a4 + e], B_data[b]);
+            }
+            if (NUMERIC) n_cbeg5 = C_indptr[row4];
         }
-        const int np = __shfl_sync(kAll, incl, 31);
-        const bool valid = lane < np;
-        // the entry of A that product `lane` belongs to = the number of entries whose products all come
-        // before it.  When no selected row of B is empty the ends of the runs are distinct, so a bit mask
-        // of them answers that with one population count; otherwise they are compared one by one.
-        int e = 0;
-        const bool in_row = lane < cur.na;
-        if (__all_sync(kAll, !in_row || cur.len > 0)) {
-            const unsigned ends = __reduce_or_sync(kAll, (in_row && incl < 32) ? (1u << incl) : 0u);
-            e = __popc(ends & (0xffffffffu >> (31 - lane)));
-        } else {
-            for (int q = 0; q < cur.na; ++q) e += (__shfl_sync(kAll, incl, q) <= lane);
+        // ---- level 4 for the row in slot 3, level 3 for slot 2, level 2 for slot 1, level 1 for a new row ----
+        I n_bb4 = 0;
+        int n_len4 = 0;
+        if (row3 >= 0 && lane < na3) {
+            n_bb4 = B_indptr[j3];
+            n_len4 = (int)((int64_t)B_indptr[j3 + 1] - (int64_t)n_bb4);
         }
-        if (!valid) e = 0;
-        const int first = __shfl_sync(kAll, incl - cur.len, e);
-        const I b0 = __shfl_sync(kAll, cur.b_begin, e);
-        uint32_t c = kEmptyKey;                        // lanes without a product share a column no row has
-        T v = (T)0;
-        if (valid) {
-            const int64_t b = (int64_t)b0 + (lane - first);
-            c = (uint32_t)B_indices[b];
-            if (NUMERIC) v = mul_rn(A_data[cur.a_begin + e], B_data[b]);
+        int64_t n_j3 = 0;
+        if (row2 >= 0 && lane < na2) n_j3 = (int64_t)A_indices[a2 + lane];
+        int64_t n_a2 = 0;
+        int n_na2 = 0;
+        if (row1 >= 0) {
+            n_a2 = (int64_t)A_indptr[row1];
+            n_na2 = (int)((int64_t)A_indptr[row1 + 1] - n_a2);
         }
-        const unsigned group = __match_any_sync(kAll, c);
-        const bool leader = valid && lane == __ffs(group) - 1;
-        const unsigned leaders = __ballot_sync(kAll, leader);
-        if (!NUMERIC) {
-            if (lane == 0) row_nnz[cur.row] = __popc(leaders);
-        } else {
-            int rank = 0;                              // position in the sorted row: leaders with a smaller column
-            for (unsigned rem = leaders; rem; rem &= rem - 1) rank += __shfl_sync(kAll, c, __ffs(rem) - 1) < c;
-            // the group's products in lane order = the reference's order of additions (0 + first + ...)
-            const int longest = __reduce_max_sync(kAll, valid ? __popc(group) : 0);
-            T sum = add_rn((T)0, v);
-            if (longest > 1) {
-                sum = (T)0;
-                unsigned rem = group;
-                for (int it = 0; it < longest; ++it) {
-                    const T t = __shfl_sync(kAll, v, rem ? __ffs(rem) - 1 : lane);
-                    if (rem) { sum = add_rn(sum, t); rem &= rem - 1; }
+        const int64_t n_row1 = idx < count ? (int64_t)list[idx] : -1;
+
+        // ---- the row whose products were requested during the previous iteration ----
+        if (row5 >= 0) {
+            const unsigned group = __match_any_sync(kAll, c5);
+            const bool leader = valid5 && lane == __ffs(group) - 1;
+            const unsigned leaders = __ballot_sync(kAll, leader);
+            if (!NUMERIC) {
+                if (lane == 0) row_nnz[row5] = __popc(leaders);
+            } else {
+                int rank = 0;                          // position in the sorted row: leaders with a smaller column
+                for (unsigned rem = leaders; rem; rem &= rem - 1) rank += __shfl_sync(kAll, c5, __ffs(rem) - 1) < c5;
+                // the group's products in lane order = the reference's order of additions (0 + first + ...)
+                const int longest = __reduce_max_sync(kAll, valid5 ? __popc(group) : 0);
+                T sum = add_rn((T)0, v5);
+                if (longest > 1) {
+                    sum = (T)0;
+                    unsigned rem = group;
+                    for (int it = 0; it < longest; ++it) {
+                        const T t = __shfl_sync(kAll, v5, rem ? __ffs(rem) - 1 : lane);
+                        if (rem) { sum = add_rn(sum, t); rem &= rem - 1; }
+                    }
+                }
+                if (leader) {
+                    C_indices[cbeg5 + rank] = (int64_t)c5;
+                    C_data[cbeg5 + rank] = sum;
                 }
             }
-            if (leader) {
-                C_indices[c_begin + rank] = (int64_t)c;
-                C_data[c_begin + rank] = sum;
-            }
         }
-        cur = nxt;
+        // ---- advance the pipeline ----
+        row5 = n_row5; cbeg5 = n_cbeg5; c5 = n_c5; v5 = n_v5; valid5 = n_valid5;
+        row4 = row3; a4 = a3; na4 = na3; bb4 = n_bb4; len4 = n_len4;
+        row3 = row2; a3 = a2; na3 = na2; j3 = n_j3;
+        row2 = row1; a2 = n_a2; na2 = n_na2;
+        row1 = n_row1;
     }
 }
 
@@ -575,7 +587,7 @@ int spgemm_symbolic(int64_t A_rows, const I* A_indices, const I* A_indptr, const
     if (!w.ok) return NB200_ERR_WORKSPACE;
     if (A_rows > 0) {
         const unsigned g = persistent_grid();
-        spgemm_warp_rows_kernel<double, I, false><<<g, 256, 0, st>>>(
+        spgemm_warp_rows_kernel<double, I, false><<<persistent_grid(kWarpRowsCtasPerSm), 256, 0, st>>>(
             w.lists, w.header + 0, nullptr, A_indices, A_indptr, nullptr, B_indices, B_indptr, w.row_nnz, nullptr, nullptr, nullptr);
 #define NB200_SYM(TEAM, SUB, TLOG, SPILL, BIN)                                                              \
         spgemm_symbolic_kernel<I, TEAM, SUB, TLOG, SPILL><<<g, 256, 0, st>>>(                                 \
@@ -610,7 +622,7 @@ int spgemm_numeric(int64_t A_rows, const T* A_data, const I* A_indices, const I*
     T* spill_vals = static_cast<T*>(spill);
     uint32_t* spill_keys = reinterpret_cast<uint32_t*>(spill_vals + (spill_slots > 0 ? spill_slots : 0));
     const unsigned g = persistent_grid();
-    spgemm_warp_rows_kernel<T, I, true><<<g, 256, 0, st>>>(
+    spgemm_warp_rows_kernel<T, I, true><<<persistent_grid(kWarpRowsCtasPerSm), 256, 0, st>>>(
         w.lists, w.header + kHdrNumBins, A_data, A_indices, A_indptr, B_data, B_indices, B_indptr, nullptr, C_indptr, C_indices, C_data);
 #define NB200_NUM(TEAM, SUB, TLOG, SPILL, BIN)                                                                   \
     spgemm_numeric_kernel<T, I, TEAM, SUB, TLOG, SPILL><<<g, 256, 0, st>>>(                                       \

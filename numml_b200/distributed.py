@@ -549,6 +549,9 @@ class DistSpMVEngine:
         self._c, self._cabi = ctypes, _cabi
         self.A = A
         self._exchange_request = os.environ.get("NB200_EXCHANGE", exchange)
+        self.use_value_symmetry = True
+        self.values_symmetric = False
+        self._side = None
         self.peer = None
         self.wait_budget_cycles = 4_000_000_000
         halo = A.halo
@@ -590,8 +593,8 @@ class DistSpMVEngine:
             if peer.usable:
                 self.peer = peer
                 self.exchange = "peer memory: neighbours' packed values read over NVLink by this library's kernels, step flags with bounded waits"
-                self.schedule = ("publish -> interior rows -> pull -> boundary rows; ghost rows -> publish -> local rows -> pull-add"
-                                 " (one stream, no communication library in the step)")
+                self.schedule = ("publish -> [pull -> boundary rows || interior rows]; [ghost rows -> publish || local rows] -> pull-add"
+                                 " (two streams, no communication library in the step)")
                 self.launches_per_step = 4 + 4
             elif self._exchange_request == "peer":
                 raise RuntimeError("the peer-memory exchange could not be set up on every rank")
@@ -665,17 +668,33 @@ class DistSpMVEngine:
         self._grad_A = [self.n, self.n_ext, self.nnz, self._p(self.idx), self._p(self.ptr), self._p(self.x_ext),
                         self._p(g), self._p(self.grad_A), self.br, self._p(self.status), self.code, self.itype, None]
         if self.fused:
-            def sym(lo, hi):
+            def sym(lo, hi, values_symmetric=0):
                 return [self.n_ext, self.nnz_ext, lo, hi, self._p(self.A.data), self._p(self.idx), self._p(self.ptr),
                         self._p(self.perm_ext), self._p(self.x_ext), self._p(self.g_ext), self._p(self.grad_A_ext),
-                        self._p(self.gx_ext), 0, self.br, self._p(self.status), self.code, self.itype, None]
+                        self._p(self.gx_ext), values_symmetric, self.br, self._p(self.status), self.code, self.itype, None]
+            # ghost rows have no values of their own and always read their mirrors through the permutation;
+            # the local rows stream their values when the local block equals its transpose in value
+            self._values_key = (self.A.data.data_ptr(), self.A.data._version)
+            self.values_symmetric = self._local_values_symmetric()
             self._sym_ghost = sym(nl, self.n_ext) if self.n_ext > nl else None
-            self._sym_local = sym(0, nl)
+            self._sym_local = sym(0, nl, int(self.values_symmetric))
         if self.peer is not None:
             self._peer_publish_x = self.peer.publish_x_args(self.x_ext)
             self._peer_pull_x = self.peer.pull_x_args(self.x_ext, self.status, self.wait_budget_cycles)
             self._peer_publish_g = self.peer.publish_g_args(self.gx_ext)
             self._peer_pull_add = self.peer.pull_add_g_args(self.gx_ext, self.status, self.wait_budget_cycles)
+
+    def _local_values_symmetric(self):
+        """True if every local entry equals its mirror image bit for bit (entries in halo columns are
+        their own mirrors in the extension): the test behind the value-symmetric backward pass, run on
+        the device.  `_prepare` repeats it whenever the values' version counter has moved; a captured
+        graph keeps the answer it was recorded with, so capture again after changing the values."""
+        if not self.use_value_symmetry:
+            return False
+        word = torch.zeros(1, dtype=torch.int32, device=self.A.data.device)
+        self._cabi.call("nb200_csr_values_symmetric", self.nnz, self._p(self.A.data), self._p(self.perm_ext), self._p(word),
+                        self.code, self.itype, self._c.c_void_p(torch.cuda.current_stream().cuda_stream))
+        return int(word.item()) == 0
 
     def close(self):
         """Release the exchange buffers (collective: a barrier first, so that no neighbour is still
@@ -685,6 +704,11 @@ class DistSpMVEngine:
             dist.barrier(group=self.A.halo.group)
             self.peer.close()
             self.peer = None
+
+    def _side_stream(self):
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.A.data.device)
+        return self._side
 
     def _launch(self, fn, args, stream):
         if args is None:
@@ -701,11 +725,19 @@ class DistSpMVEngine:
         lib = self._lib
         stream = self._c.c_void_p(torch.cuda.current_stream().cuda_stream)
         if self.peer is not None:
+            # the small kernels (pull, boundary rows) go to a side stream and are issued first, so that they
+            # take their few SMs at once and run under the cover of the interior rows
+            main = torch.cuda.current_stream()
+            side = self._side_stream()
             self._launch(lib.nb200_halo_publish, self._peer_publish_x, stream)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                s2 = self._c.c_void_p(side.cuda_stream)
+                self._launch(lib.nb200_halo_pull, self._peer_pull_x, s2)
+                for args in self._fwd_boundary:
+                    self._launch(lib.nb200_spgemv_forward, args, s2)
             self._launch(lib.nb200_spgemv_forward, self._fwd_interior, stream)
-            self._launch(lib.nb200_halo_pull, self._peer_pull_x, stream)
-            for args in self._fwd_boundary:
-                self._launch(lib.nb200_spgemv_forward, args, stream)
+            main.wait_stream(side)
             return self.y
         for args in self._pack:
             self._launch(lib.nb200_gather, args, stream)
@@ -757,16 +789,24 @@ class DistSpMVEngine:
         if self.fused and g.data_ptr() != self.g_ext.data_ptr():
             self.g_ext[:self.n].copy_(g)            # callers may also write into g_ext[:n] directly
             g = self.g_ext[:self.n]
-        if not hasattr(self, "_lib") or self._g.data_ptr() != g.data_ptr():
+        if not hasattr(self, "_lib") or self._g.data_ptr() != g.data_ptr() or \
+                (self.fused and self._values_key != (self.A.data.data_ptr(), self.A.data._version)):
             self._prepare(g)
         lib, halo = self._lib, self.A.halo
         stream = self._c.c_void_p(torch.cuda.current_stream().cuda_stream)
         # partial sums for halo columns first, so that their exchange overlaps the rest
         if self.peer is not None:
             if self.fused:
-                self._launch(lib.nb200_spgemv_backward_symmetric_rows, self._sym_ghost, stream)
-                self._launch(lib.nb200_halo_publish, self._peer_publish_g, stream)
+                # ghost rows and the publication of their partial sums run beside the local rows
+                main = torch.cuda.current_stream()
+                side = self._side_stream()
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    s2 = self._c.c_void_p(side.cuda_stream)
+                    self._launch(lib.nb200_spgemv_backward_symmetric_rows, self._sym_ghost, s2)
+                    self._launch(lib.nb200_halo_publish, self._peer_publish_g, s2)
                 self._launch(lib.nb200_spgemv_backward_symmetric_rows, self._sym_local, stream)
+                main.wait_stream(side)
             else:
                 self._launch(lib.nb200_spgemv_forward, self._t_halo, stream)
                 self._launch(lib.nb200_halo_publish, self._peer_publish_g, stream)

@@ -48,7 +48,10 @@ def build(reference=DEFAULT_REFERENCE, force=False, verbose=True):
 
     os.makedirs(OUT_DIR, exist_ok=True)
     objs = []
-    common = ["g++", "-std=c++17", "-DCUDA_ENABLED=0", "-O2", "-fPIC", "-w",
+    # -DNDEBUG is what a setuptools build of the reference passes (it comes with the interpreter's own
+    # compile flags, sysconfig OPT); without it an assert in the reference's queue (cpp/vector_queue.hpp:20,
+    # a "full" test that fires as soon as the queue holds one element) aborts its sparse LU.
+    common = ["g++", "-std=c++17", "-DCUDA_ENABLED=0", "-DNDEBUG", "-O2", "-fPIC", "-w",
               "-DTORCH_EXTENSION_NAME=" + MODULE, "-DTORCH_API_INCLUDE_EXTENSION_H",
               "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
     incs = ["-I" + p for p in include_paths()] + ["-I" + sysconfig.get_paths()["include"],

@@ -190,6 +190,38 @@ def splincomb_backward(rows, cols, alpha, A_data, A_indices, A_indptr, beta, B_d
     return [grad_A, grad_B]
 
 
+def splu(rows, cols, data, indices, indptr):
+    """Sparse LU without pivoting, as the reference's splu (cpp/sparse_csr_cpu.cpp:778-1017): returns
+    ``[M_data, M_indices, M_indptr, Mt_data, Mt_indices, Mt_indptr]`` with M = L + U (unit lower L, its
+    ones not stored) on the filled pattern and Mt its transpose."""
+    data, indices, indptr = _c(data), _c(indices, torch.int64), _c(indptr, torch.int64)
+    n = rows
+    lib().oracle_splu_symbolic.restype = ctypes.c_int64
+    M_indptr = torch.empty(n + 1, dtype=torch.int64)
+    nnz = lib().oracle_splu_symbolic(_i(n), _p(indices), _p(indptr), _p(M_indptr), None, None)
+    M_indices = torch.empty(nnz, dtype=torch.int64)
+    is_fill = torch.empty(nnz, dtype=torch.int32)
+    lib().oracle_splu_symbolic(_i(n), _p(indices), _p(indptr), _p(M_indptr), _p(M_indices), _p(is_fill))
+    # values of A on the filled pattern, explicit zeros where fill is introduced
+    M_data = torch.zeros(nnz, dtype=data.dtype)
+    M_data[is_fill == 0] = data
+    Mt_data, Mt_indices, Mt_indptr, _ = csr_transpose_forward(n, n, M_data, M_indices, M_indptr)
+    getattr(lib(), "oracle_splu_numeric_" + _sfx(data))(_i(n), _p(Mt_data), _p(Mt_indices), _p(Mt_indptr))
+    M_data, M_indices, M_indptr, _ = csr_transpose_forward(n, n, Mt_data, Mt_indices, Mt_indptr)
+    return [M_data, M_indices, M_indptr, Mt_data, Mt_indices, Mt_indptr]
+
+
+def spsolve_backward(grad_x, x, rows, cols, Mt_data, Mt_indices, Mt_indptr, A_data, A_indices, A_indptr):
+    """grad_b = A^{-T} grad_x by two triangular solves with the transposed factors, grad_A = -(grad_b x^T)
+    on the pattern of A (reference cpp/sparse_csr_cpu.cpp:1019-1052)."""
+    y = sptrsv_forward(rows, cols, Mt_data, Mt_indices, Mt_indptr, True, False, grad_x)
+    grad_b = sptrsv_forward(rows, cols, Mt_data, Mt_indices, Mt_indptr, False, True, y)
+    A_indices, A_indptr, x = _c(A_indices, torch.int64), _c(A_indptr, torch.int64), _c(x)
+    row_of = torch.repeat_interleave(torch.arange(rows), A_indptr[1:] - A_indptr[:-1])
+    grad_A = -(grad_b[row_of] * x[A_indices])
+    return [grad_A, grad_b]
+
+
 def triangle(rows, data, indices, indptr, k, lower):
     """tril (``lower``) / triu of a CSR matrix with ascending columns per row, as the reference's Python
     loops compute it (numml/sparse/_csr.py:234-330): entries with column <= row + k (>= row + k), in

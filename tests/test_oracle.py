@@ -152,6 +152,35 @@ def test_pattern_operators_match_the_reference(oracle, reference_module, dtype):
             assert torch.equal(d[pos], td)
 
 
+def test_sparse_lu_matches_the_reference(oracle, reference_module):
+    """LU without pivoting (fill pattern, factors, their transposes) and the backward of the direct
+    solve, bit for bit against the compiled reference, plus L U = A."""
+    import numpy as np
+    import scipy.sparse as sps
+    cases = [sps.random(60, 60, density=0.08, random_state=3, format="csr") + sps.eye(60) * 4,
+             sps.diags([-1, 2, -1], [-1, 0, 1], shape=(40, 40), format="csr")]
+    pd, pi, pp, (m, k) = W.poisson2d_5pt(8, torch.float64)
+    cases.append(sps.csr_matrix((pd.numpy(), pi.numpy(), pp.numpy()), shape=(m, k)))
+    for S in cases:
+        S = S.tocsr()
+        S.sort_indices()
+        n = S.shape[0]
+        d = torch.from_numpy(S.data.astype(np.float64))
+        i, p = torch.from_numpy(S.indices.astype(np.int64)), torch.from_numpy(S.indptr.astype(np.int64))
+        mine = oracle.splu(n, n, d, i, p)
+        M = sps.csr_matrix((mine[0].numpy(), mine[1].numpy(), mine[2].numpy()), shape=(n, n))
+        L, U = sps.tril(M, -1) + sps.eye(n), sps.triu(M)
+        assert abs(L @ U - S).max() < 1e-12
+        x, gx = W.randn(n, 1, torch.float64), W.randn(n, 2, torch.float64)
+        gmine = oracle.spsolve_backward(gx, x, n, n, mine[3], mine[4], mine[5], d, i, p)
+        if reference_module is not None:
+            for u, v in zip(reference_module.splu(n, n, d, i, p), mine):
+                assert_same(u, v)
+            ref = reference_module.spsolve_backward(gx, x, n, n, mine[3], mine[4], mine[5], d, i, p)
+            assert_same(ref[0], gmine[0])
+            assert_same(ref[1], gmine[1])
+
+
 def test_workload_sizes():
     assert W.poisson2d_5pt(256)[0].numel() == 326656
     assert W.poisson3d_7pt(16)[0].numel() == 7 * 16 ** 3 - 6 * 16 ** 2
