@@ -374,6 +374,31 @@ NB200_API int nb200_cg_fixed_iterations(int64_t n, int64_t nnz, const void* data
                                         int dtype, int itype, nb200_stream stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Row-partitioned CG, the part of an iteration that is not the SpMV.  No counterpart in the reference
+ * (numml/krylov.py:83-155 is a single-device loop); the recurrence is the same.  Every rank holds a block
+ * of b, x, r, p and calls the phases in this order, the SpMV Ap = A p (halo exchange + local kernels)
+ * being the caller's between 4 and 2:
+ *     0  r = b, p = r, x = 0; local <r,r> published        1  total <r,r> -> history[0]
+ *     2  local <Ap,p> published                             3  alpha from the total; x += alpha p; r -= alpha Ap;
+ *     4  beta from the total <r,r>; p = r + beta p;            local <r,r> published
+ *        history[it+1]; the iteration counter moves on
+ * A dot product is reduced across ranks through peer memory, inside these kernels: the last block of the
+ * kernel that forms the local sum stores it into this rank's scalar area and sets this rank's flag to the
+ * reduction's sequence number (release, system scope); the next kernel starts by waiting (bounded by
+ * `wait_budget_cycles`, NB200_ERR_WAIT_BUDGET in `status` and NaN totals on expiry) for every rank's flag
+ * and adds the ranks' sums in rank order, so all ranks get the same bits.  `table` (device, 2 int64 per
+ * rank) holds the address of each rank's scalar area (2 halves of 4 doubles, alternating by sequence
+ * number) and of its flag word, as mapped into this process; `sequence_word` is a device word of this
+ * rank that lives as long as the exchange buffers (zero when they are created).  world <= 32.
+ * `workspace`: nb200_cg_peer_workspace_bytes() bytes, kept for the whole solve.
+ * ------------------------------------------------------------------------------------------- */
+NB200_API size_t nb200_cg_peer_workspace_bytes(void);
+NB200_API int nb200_cg_peer_phase(int phase, int64_t n, const void* b, void* x, void* r, void* p, const void* Ap,
+                                  void* residual_history, void* workspace, size_t workspace_bytes,
+                                  int world, int rank, const int64_t* table, int32_t* sequence_word,
+                                  int32_t* status, int64_t wait_budget_cycles, int dtype, nb200_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Pattern-building operators (all index arrays int64, as the matrices store them).  Each produces a new
  * pattern in two steps: a count call that writes the new row pointers (the caller reads the last one, a
  * device-to-host copy of 8 bytes, to size the outputs) and a fill call.  `workspace` must hold
@@ -416,6 +441,32 @@ NB200_API size_t nb200_coo_workspace_bytes(int64_t n);
 NB200_API int nb200_coo_to_csr(int64_t n, const int64_t* row_ind, const int64_t* col_ind, int64_t nrows, int64_t ncols,
                                int sort_columns, int64_t* perm, int64_t* indptr, void* workspace, size_t workspace_bytes,
                                nb200_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Sparse LU without pivoting, M = L + U with unit lower L (its ones not stored).  Replaces splu (reference
+ * cpp/sparse_csr.hpp:107-111, CPU cpp/sparse_csr_cpu.cpp:778-1017, CUDA cpp/sparse_csr_cuda.cu:870-1268);
+ * with the triangular solve and nb200_masked_outer it also gives spsolve and spsolve_backward
+ * (cpp/sparse_csr.hpp:113-118, CPU :1019-1052).  Index arrays int64; every row of A must store its diagonal.
+ *
+ * nb200_splu_symbolic_count  pattern of M by the fill2 traversal (one warp per row): row pointers into
+ *                            M_indptr (n+1 int64; the caller reads the last one to size M).
+ * nb200_splu_symbolic_fill   M_indices (ascending per row) and M_data = the value of A, or 0 for fill.
+ * nb200_splu_numeric         in place on the TRANSPOSE of M (Mt_*: columns of M stored as rows, e.g. from
+ *                            nb200_csr_transpose_structure + nb200_gather): left-looking elimination, one
+ *                            warp per column, a flag per column (`done`, n int32) with bounded polls;
+ *                            NB200_ERR_WAIT_BUDGET in `status` if a wait runs out.  Every update is an
+ *                            unfused multiply and subtract applied in the reference's order: bit-identical.
+ * `workspace`: nb200_splu_workspace_bytes(n) bytes for the two symbolic calls (three stamp arrays of n
+ * words per row in flight, at most about 2 GiB).  n < 2^30.
+ * ------------------------------------------------------------------------------------------- */
+NB200_API size_t nb200_splu_workspace_bytes(int64_t n);
+NB200_API int nb200_splu_symbolic_count(int64_t n, const int64_t* A_indices, const int64_t* A_indptr, int64_t* M_indptr,
+                                        void* workspace, size_t workspace_bytes, nb200_stream stream);
+NB200_API int nb200_splu_symbolic_fill(int64_t n, const void* A_data, const int64_t* A_indices, const int64_t* A_indptr,
+                                       const int64_t* M_indptr, int64_t* M_indices, void* M_data,
+                                       void* workspace, size_t workspace_bytes, int dtype, nb200_stream stream);
+NB200_API int nb200_splu_numeric(int64_t n, void* Mt_data, const int64_t* Mt_indices, const int64_t* Mt_indptr,
+                                 int32_t* done, int32_t* status, int64_t wait_budget_cycles, int dtype, nb200_stream stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Halo exchange of a row-partitioned SpMV over peer memory.  No counterpart in the reference, which has

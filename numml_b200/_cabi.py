@@ -53,6 +53,8 @@ SIGNATURES = {
     "nb200_cg_fixed_iterations": (_int, [_i64, _i64, _vp, _vp, _vp, _int, _vp, _vp, _int, _vp, _i64, _vp, _sz, _vp,
                                          _int, _int, _vp]),
     "nb200_masked_outer": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _c.c_double, _vp, _int, _int, _vp]),
+    "nb200_cg_peer_workspace_bytes": (_sz, []),
+    "nb200_cg_peer_phase": (_int, [_int, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _int, _int, _vp, _vp, _vp, _i64, _int, _vp]),
     "nb200_pattern_workspace_bytes": (_sz, [_i64]),
     "nb200_csr_triangle_count": (_int, [_i64, _vp, _vp, _i64, _int, _vp, _vp, _sz, _vp]),
     "nb200_csr_triangle_fill": (_int, [_i64, _vp, _vp, _vp, _i64, _int, _vp, _vp, _vp, _vp, _int, _vp]),
@@ -61,6 +63,10 @@ SIGNATURES = {
     "nb200_csr_lincomb_backward": (_int, [_i64, _c.c_double, _vp, _vp, _c.c_double, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
     "nb200_coo_workspace_bytes": (_sz, [_i64]),
     "nb200_coo_to_csr": (_int, [_i64, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _sz, _vp]),
+    "nb200_splu_workspace_bytes": (_sz, [_i64]),
+    "nb200_splu_symbolic_count": (_int, [_i64, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "nb200_splu_symbolic_fill": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _int, _vp]),
+    "nb200_splu_numeric": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp]),
     "nb200_halo_publish": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _int, _vp, _int, _vp]),
     "nb200_halo_pull": (_int, [_int, _vp, _i64, _vp, _vp, _vp, _i64, _int, _vp]),
     "nb200_halo_pull_add": (_int, [_int, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp]),

@@ -396,7 +396,9 @@ class PeerExchange:
     """Exchange buffers of the peer-memory halo exchange (``csrc/halo.cu``): one buffer per rank,
     created by ``nb200_ipc_alloc``, mapped by every neighbour with CUDA IPC.
 
-    Layout of a buffer (bytes): ``[flag words: 256][packed x values: 2 halves][partial sums: 2 halves]``.
+    Layout of a buffer (bytes): ``[flag words and scalar area: 256][packed x values: 2 halves][partial sums:
+    2 halves]``; the first 256 bytes hold the three flag words (x, grad_x, scalar reductions) at offsets
+    0, 4, 8 and, at offset 64, two halves of four doubles for dot products reduced across ranks.
     The packed x area holds, for every neighbour in ascending order, the entries of this rank's block
     of x that the neighbour reads; the partial-sum area holds this rank's grad_x contributions to the
     halo columns in halo-slot order (neighbour by neighbour, ascending).  The constructor is collective
@@ -405,6 +407,7 @@ class PeerExchange:
     """
 
     FLAG_BYTES = 256
+    SCALAR_OFFSET = 64
 
     def __init__(self, halo, dtype, device):
         import ctypes
@@ -459,7 +462,10 @@ class PeerExchange:
             self.close()
             return
         self.peers = peers
+        self._handles = {r: metas[r]["handle"] for r in range(halo.world)}
         dev = device
+        self.reduce_seq = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._reduce_table = None
         self.step_word = torch.zeros(1, dtype=torch.int32, device=dev)
         self.arrivals = torch.zeros(1, dtype=torch.int32, device=dev)
         # what is packed for the neighbours: their segments, concatenated in ascending order
@@ -515,6 +521,29 @@ class PeerExchange:
         return [len(self.halo.peers_out), self._p(self.g_desc), int(self.targets.numel()), self._p(self.targets),
                 self._p(self.target_ptr), self._p(self.src_peer), self._p(self.src_elem), self._p(grad_x),
                 self._p(self.step_word), self._p(status), budget, self.code, None]
+
+    def reduce_table(self):
+        """Device table for reductions across all ranks (``nb200_cg_peer_phase``): per rank the address of
+        its scalar area and of its reduction flag.  Maps the buffers of the ranks that are not halo
+        neighbours on first use."""
+        if self._reduce_table is None:
+            halo, lib, c = self.halo, self._cabi.lib(), self._c
+            words = []
+            with torch.cuda.device(self.device):
+                for r in range(halo.world):
+                    if r == halo.rank:
+                        base = self.base
+                    else:
+                        if r not in self.mapped:
+                            ptr = c.c_void_p()
+                            buf = (c.c_ubyte * 64).from_buffer_copy(self._handles[r])
+                            if lib.nb200_ipc_open(buf, c.byref(ptr)) != 0:
+                                raise RuntimeError(f"could not map the exchange buffer of rank {r}")
+                            self.mapped[r] = ptr.value
+                        base = self.mapped[r]
+                    words += [base + self.SCALAR_OFFSET, base + 8]
+            self._reduce_table = torch.tensor(words, dtype=torch.int64, device=self.device)
+        return self._reduce_table
 
     def close(self):
         """Unmap the neighbours' buffers and free this rank's (after a barrier by the caller, so that no
@@ -832,16 +861,25 @@ class DistSpMVEngine:
 
 class DistCG:
     """Unpreconditioned CG with a fixed iteration count on a row-partitioned SPD matrix, driven through a
-    ``DistSpMVEngine``: the SpMV of every iteration is the engine's forward (halo values over peer memory
-    or NCCL, overlapped with the rows that do not need them), the vector updates are this rank's block
-    only, and the two dot products of an iteration are all-reduced.  The recurrence is the reference's
-    (``numml/krylov.py:135-153``) with ``rtol = 0``; nothing is read back to the host inside the loop."""
+    ``DistSpMVEngine``.  The recurrence is the reference's (``numml/krylov.py:135-153``) with ``rtol = 0``;
+    nothing is read back to the host inside the loop.
+
+    With the peer-memory exchange the whole iteration is this library's kernels: the engine's forward
+    (publish, [pull and boundary rows beside] the interior rows) and three vector kernels whose dot
+    products are reduced across ranks through the exchange buffers, in rank order, inside the kernels
+    (``nb200_cg_peer_phase``).  One iteration is recorded into a CUDA graph and replayed.  Without it the
+    vector updates are torch operations and the two dot products of an iteration are all-reduced."""
 
     def __init__(self, engine):
         self.engine = engine
         self.group = engine.A.halo.group
-        self.schedule = ("per iteration: engine forward (" + ("peer-memory" if engine.peer is not None else "NCCL")
-                         + " halo exchange) + vector updates + 2 all-reduced dot products; no host synchronisation")
+        self.peer = engine.peer is not None and engine.A.halo.world <= 32
+        self._graph = None
+        if self.peer:
+            self.schedule = ("per iteration: publish p, [pull + boundary rows || interior rows], <Ap,p>, update with <r,r>, direction;"
+                             " dot products reduced through peer memory inside the kernels; one CUDA graph per iteration")
+        else:
+            self.schedule = "per iteration: engine forward (NCCL halo exchange) + torch vector updates + 2 all-reduced dot products"
 
     def _dot(self, a, b):
         s = torch.dot(a, b)
@@ -850,6 +888,8 @@ class DistCG:
 
     def solve(self, b_local, iterations):
         """Returns (this rank's block of x, the iterations + 1 residual norms)."""
+        if self.peer:
+            return self._solve_peer(b_local, iterations)
         eng = self.engine
         nl = eng.A.halo.n_local
         p = eng.x_ext[:nl]                      # the search direction lives where the engine reads x
@@ -873,3 +913,56 @@ class DistCG:
             hist[it + 1] = torch.sqrt(rz)
         return x, hist
 
+    def _solve_peer(self, b_local, iterations):
+        import ctypes
+        from . import _cabi
+        eng, halo = self.engine, self.engine.A.halo
+        dev, dt = b_local.device, b_local.dtype
+        nl = halo.n_local
+        P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+        if not hasattr(self, "_work"):
+            wbytes = _cabi.lib().nb200_cg_peer_workspace_bytes()
+            self._work = torch.zeros(wbytes, dtype=torch.uint8, device=dev)
+            self._wbytes = wbytes
+            self._x = torch.empty(nl, dtype=dt, device=dev)
+            self._r = torch.empty(nl, dtype=dt, device=dev)
+            self._b = torch.empty(nl, dtype=dt, device=dev)
+            self._table = eng.peer.reduce_table()
+        if getattr(self, "_hist", None) is None or self._hist.numel() != iterations + 1:
+            self._hist = torch.empty(iterations + 1, dtype=dt, device=dev)
+            self._graph = None                                   # the history buffer is part of the recording
+        self._b.copy_(b_local)
+        p = eng.x_ext[:nl]
+        code = _cabi.F64 if dt == torch.float64 else _cabi.F32
+
+        def phase(k, Ap=None):
+            _cabi.call("nb200_cg_peer_phase", k, nl, P(self._b), P(self._x), P(self._r), P(p),
+                       P(Ap) if Ap is not None else None, P(self._hist), P(self._work), self._wbytes, halo.world, halo.rank,
+                       P(self._table), P(eng.peer.reduce_seq), P(eng.status), eng.wait_budget_cycles, code,
+                       ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+
+        def iteration():
+            Ap = eng.forward()
+            phase(2, Ap)
+            phase(3, Ap)
+            phase(4)
+
+        phase(0)
+        phase(1)
+        if self._graph is None and iterations > 1:
+            # one eager iteration warms everything up; the recording then covers one iteration
+            iteration()
+            done = 1
+            torch.cuda.synchronize(dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                iteration()
+            self._graph = graph
+        else:
+            done = 0
+        for _ in range(iterations - done):
+            if self._graph is not None:
+                self._graph.replay()
+            else:
+                iteration()
+        return self._x.clone(), self._hist.clone()

@@ -525,3 +525,58 @@ def coo_to_csr_order(row_ind, col_ind, nrows, ncols, sort_columns=True):
                    _ptr(indptr), _ptr(work), wbytes, _stream())
     return perm, indptr
 
+
+# -------------------------------------------------------------------------------------------------
+# Sparse LU and the direct solve                      reference cpp/sparse_csr.hpp:107-118
+# -------------------------------------------------------------------------------------------------
+def splu(A_rows, A_cols, A_data, A_indices, A_indptr):
+    """LU without pivoting on the filled pattern.  Returns ``[M_data, M_indices, M_indptr, Mt_data,
+    Mt_indices, Mt_indptr]`` like the reference: M = L + U (unit lower L, ones not stored) and its transpose."""
+    dev = _require_cuda(A_data, A_indices, A_indptr)
+    if A_rows != A_cols:
+        raise RuntimeError(f"LU factorisation needs a square matrix, got {A_rows} x {A_cols}")
+    A_data = _values(A_data)
+    A_indices, A_indptr = _index_tensor(A_indices), _index_tensor(A_indptr)
+    plan = _plan.get_plan(A_rows, A_cols, A_indices, A_indptr)
+    plan.require(sorted_columns=True, diagonal=True, what="the LU factorisation")
+    n = A_rows
+    code = _dtype_code(A_data)
+    with _on(dev):
+        wbytes = _cabi.lib().nb200_splu_workspace_bytes(n)
+        work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+        M_indptr = torch.empty(n + 1, dtype=torch.int64, device=dev)
+        _cabi.call("nb200_splu_symbolic_count", n, _ptr(A_indices), _ptr(A_indptr), _ptr(M_indptr), _ptr(work), wbytes, _stream())
+        nnz_m = int(M_indptr[-1].item())
+        M_indices = torch.empty(nnz_m, dtype=torch.int64, device=dev)
+        M_data = torch.empty(nnz_m, dtype=A_data.dtype, device=dev)
+        _cabi.call("nb200_splu_symbolic_fill", n, _ptr(A_data), _ptr(A_indices), _ptr(A_indptr), _ptr(M_indptr),
+                   _ptr(M_indices), _ptr(M_data), _ptr(work), wbytes, code, _stream())
+        del work
+        Mt_data, Mt_indices, Mt_indptr, perm = csr_transpose_forward(n, n, M_data, M_indices, M_indptr)
+        done = torch.empty(n, dtype=torch.int32, device=dev)
+        status = _status_word(dev)
+        _cabi.call("nb200_splu_numeric", n, _ptr(Mt_data), _ptr(Mt_indices), _ptr(Mt_indptr), _ptr(done), _ptr(status),
+                   int(sptrsv_wait_budget_cycles), code, _stream())
+        check_status(dev)
+        # back to rows: entry q of the transpose is entry perm[q] of M
+        _cabi.call("nb200_scatter", nnz_m, _ptr(Mt_data), _ptr(perm), _ptr(M_data), code, _cabi.I64, _stream())
+    return [M_data, M_indices, M_indptr, Mt_data, Mt_indices, Mt_indptr]
+
+
+def spsolve_backward(grad_x, x, A_rows, A_cols, Mt_data, Mt_indices, Mt_indptr, A_data, A_indices, A_indptr):
+    """grad_b = A^{-T} grad_x by two triangular solves with the transposed factors (U^T is lower with the
+    pivots on its diagonal, L^T is unit upper); grad_A = -(grad_b x^T) on the pattern of A."""
+    y = sptrsv_forward(A_rows, A_cols, Mt_data, Mt_indices, Mt_indptr, True, False, grad_x)
+    grad_b = sptrsv_forward(A_rows, A_cols, Mt_data, Mt_indices, Mt_indptr, False, True, y)
+    dev = _require_cuda(A_data, A_indices, A_indptr, x)
+    A_data = _values(A_data)
+    x = _rhs(x, A_rows, A_data)
+    plan = _plan.get_plan(A_rows, A_cols, _index_tensor(A_indices), _index_tensor(A_indptr))
+    idx, ptr, itype = plan.csr()
+    nrhs = 1 if x.ndim == 1 else int(x.shape[1])
+    with _on(dev):
+        grad_A = torch.empty_like(A_data)
+        _cabi.call("nb200_masked_outer", A_rows, plan.nnz, nrhs, _ptr(idx), _ptr(ptr), _ptr(grad_b), _ptr(x), -1.0,
+                   _ptr(grad_A), _dtype_code(A_data), itype, _stream())
+    return [grad_A, grad_b]
+

@@ -90,10 +90,12 @@ def test_accelerated_operators_refuse_cpu_tensors():
         A @ "x"
 
 
-def test_lu_is_out_of_scope():
+def test_lu_has_no_cpu_path():
     import numml_b200.sparse.linalg as spla
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(RuntimeError, match="CUDA"):
         spla.splu(sp.eye(3))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        spla.spsolve(sp.eye(3), torch.ones(3))
 
 
 def test_linear_operator_and_profiler(capsys):
