@@ -73,10 +73,48 @@ def build(force=False, verbose=False, ptxas_info=False):
     return LIB_PATH
 
 
+EXT_SRC = os.path.join(PKG, "csrc_ext", "ops_ext.cpp")
+EXT_NAME = "numml_b200_ext"
+
+
+def extension_path():
+    import sysconfig
+    return os.path.join(LIB_DIR, EXT_NAME + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_extension(force=False, verbose=False):
+    """Compile the torch extension with the per-call path of the SpMV / SpMM operators
+    (``csrc_ext/ops_ext.cpp``) against the installed torch and link it to ``libnumml_b200.so`` (found at
+    run time next to itself).  Returns its path."""
+    import sysconfig
+    import torch
+    from torch.utils.cpp_extension import include_paths, library_paths
+    build()
+    out = extension_path()
+    newest = max(os.path.getmtime(EXT_SRC), os.path.getmtime(HEADER))
+    if os.path.exists(out) and not force and os.path.getmtime(out) >= newest:
+        return out
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    incs = ["-I" + p for p in include_paths()] + ["-I" + sysconfig.get_paths()["include"], "-I" + os.path.join(cuda_home, "include")]
+    libdirs = library_paths()
+    cmd = (["g++", "-std=c++17", "-O2", "-fPIC", "-w", "-shared", "-DNDEBUG", "-DTORCH_EXTENSION_NAME=" + EXT_NAME,
+            "-DTORCH_API_INCLUDE_EXTENSION_H", "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
+           + incs + [EXT_SRC, "-o", out] + ["-L" + d for d in libdirs] + ["-Wl,-rpath," + d for d in libdirs]
+           + ["-L" + LIB_DIR, "-Wl,-rpath,$ORIGIN", "-lnumml_b200", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda",
+              "-ltorch", "-ltorch_python"])
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.check_call(cmd)
+    return out
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--ptxas-info", action="store_true", help="print registers / spills / shared memory per kernel")
+    ap.add_argument("--no-extension", action="store_true", help="skip the compiled operator shim")
     a = ap.parse_args()
     print(build(a.force, a.verbose, a.ptxas_info))
+    if not a.no_extension:
+        print(build_extension(a.force, a.verbose))

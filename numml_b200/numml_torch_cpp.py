@@ -24,6 +24,10 @@ spmv_kernel = "auto"
 # Whether the one-pass backward may use the value-symmetric variant (the matrix equals its transpose
 # in value too, established by a cached device-side test; see PatternPlan.values_symmetric).
 spmv_value_symmetry = True
+# Whether SpMV / SpMM calls go through the compiled torch extension (numml_b200/csrc_ext/ops_ext.cpp:
+# argument checks, allocation, plan lookup and the C-ABI call in C++) when it has been built.  The
+# functions below do the same work in Python and are what runs otherwise; results are identical.
+use_compiled_shim = True
 
 
 def _dtype_code(t):
@@ -102,9 +106,72 @@ def _status_word(dev):
 
 
 # -------------------------------------------------------------------------------------------------
+# Compiled per-call path
+# -------------------------------------------------------------------------------------------------
+_ext = None
+_ext_tried = False
+
+
+def _planner(rows, cols, indices, indptr, transpose):
+    """What the compiled shim caches per sparsity pattern (called by it on a cache miss)."""
+    plan = _plan.get_plan(rows, cols, indices, indptr)
+    idx, ptr, itype = plan.csr()
+    dev = indices.device
+    with _on(dev):
+        out = {"idx": idx, "ptr": ptr, "itype": itype, "block_rows": plan.spmv_block_rows(), "status": _status_word(dev),
+               "row_order": plan.spmm_row_order(), "t_indptr": None}
+        if transpose:
+            t_indptr, t_indices, t_perm, _ = plan.transpose()
+            out.update(t_indptr=t_indptr, t_indices=t_indices, t_perm=t_perm,
+                       t_block_rows=plan.spmv_block_rows(transposed=True), pattern_symmetric=plan.pattern_symmetric(),
+                       t_row_order=plan.spmm_row_order(transposed=True))
+    return out
+
+
+def compiled_shim():
+    """The extension module, or None when it has not been built (or has been switched off)."""
+    global _ext, _ext_tried
+    if not use_compiled_shim:
+        return None
+    if not _ext_tried:
+        _ext_tried = True
+        import importlib.util
+        import os
+        from . import build as _build
+        path = _build.extension_path()
+        if os.path.exists(path):
+            _cabi.lib()                                  # the CUDA library first: the extension links against it
+            spec = importlib.util.spec_from_file_location(_build.EXT_NAME, path)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            mod.set_planner(_planner)
+            _ext = mod
+    return _ext
+
+
+def _flags():
+    if spmv_backward_mode not in ("transpose", "atomic"):
+        raise RuntimeError(f"unknown spmv_backward_mode {spmv_backward_mode!r}")
+    return (1 if spmv_kernel == "auto" else 0) | (2 if spmv_backward_mode == "transpose" else 0) | (4 if spmv_value_symmetry else 0)
+
+
+def values_symmetric_state(rows, cols, indices, indptr):
+    """What is known about the value symmetry of the last values used with this pattern in spgemv_backward:
+    None (nothing tested yet), True or False."""
+    ext = compiled_shim()
+    if ext is not None:
+        return {1: True, 2: False}.get(ext.values_state(indices, indptr))
+    state = _plan.get_plan(rows, cols, indices, indptr).extra.get("values_symmetric")
+    return None if state is None else state[1]
+
+
+# -------------------------------------------------------------------------------------------------
 # SpMV                                               reference cpp/sparse_csr.hpp:32-42
 # -------------------------------------------------------------------------------------------------
 def spgemv_forward(A_rows, A_cols, A_data, A_col_ind, A_rowptr, x):
+    ext = compiled_shim()
+    if ext is not None:
+        return ext.spgemv_forward(A_rows, A_cols, A_data, A_col_ind, A_rowptr, x, _flags())
     dev = _require_cuda(A_data, A_col_ind, A_rowptr, x)
     A_data = _values(A_data)
     x = _values(x, A_data)
@@ -119,6 +186,9 @@ def spgemv_forward(A_rows, A_cols, A_data, A_col_ind, A_rowptr, x):
 
 
 def spgemv_backward(grad_z, A_rows, A_cols, A_data, A_col_ind, A_rowptr, x):
+    ext = compiled_shim()
+    if ext is not None:
+        return ext.spgemv_backward(grad_z, A_rows, A_cols, A_data, A_col_ind, A_rowptr, x, _flags())
     dev = _require_cuda(grad_z, A_data, A_col_ind, A_rowptr, x)
     A_data = _values(A_data)
     x = _values(x, A_data)
@@ -189,6 +259,9 @@ def _dense(t, like):
 
 
 def spdmm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B):
+    ext = compiled_shim()
+    if ext is not None:
+        return ext.spdmm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B)
     dev = _require_cuda(A_data, A_indices, A_indptr, B)
     A_data = _values(A_data)
     B = _dense(B, A_data)
@@ -206,6 +279,9 @@ def spdmm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B):
 
 
 def spdmm_backward(A_rows, A_cols, A_data, A_indices, A_indptr, B, grad_C):
+    ext = compiled_shim()
+    if ext is not None:
+        return ext.spdmm_backward(A_rows, A_cols, A_data, A_indices, A_indptr, B, grad_C)
     dev = _require_cuda(A_data, A_indices, A_indptr, B, grad_C)
     A_data = _values(A_data)
     B = _dense(B, A_data)

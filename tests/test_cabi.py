@@ -42,3 +42,21 @@ def test_argument_validation_needs_no_gpu():
     handle = _cabi.lib()
     assert handle.nb200_spgemv_forward(-1, 1, 0, None, None, None, None, None, None, 0, None, 1, 1, None) == 1
     assert handle.nb200_gather(-5, None, None, None, 0, 0, None) == 1
+
+
+def test_compiled_shim_builds_and_refuses_cpu_tensors():
+    """The torch extension with the per-call path of the SpMV / SpMM operators compiles against the
+    installed torch, links to the CUDA library, imports without a GPU, and (like the Python shim)
+    raises on CPU tensors instead of computing anything."""
+    import pytest
+    import torch
+    from numml_b200 import numml_torch_cpp as ops
+    assert os.path.exists(build.build_extension())
+    ext = ops.compiled_shim()
+    assert ext is not None and ext.library_version() == _cabi.lib().nb200_version()
+    d, i, p, x = torch.ones(2), torch.zeros(2, dtype=torch.long), torch.tensor([0, 1, 2]), torch.ones(2)
+    for call in (lambda: ops.spgemv_forward(2, 2, d, i, p, x), lambda: ops.spgemv_backward(x, 2, 2, d, i, p, x),
+                 lambda: ops.spdmm_forward(2, 2, d, i, p, torch.ones(2, 3)),
+                 lambda: ops.spdmm_backward(2, 2, d, i, p, torch.ones(2, 3), torch.ones(2, 3))):
+        with pytest.raises(RuntimeError, match="CUDA"):
+            call()

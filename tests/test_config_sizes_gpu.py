@@ -83,9 +83,7 @@ def test_c2_poisson3d_128_fp64_spmv(oracle, spmv_ops, poisson128, values):
         assert_same(gA_ref, gA, f"grad_A (call {call})")
         assert_same(gx_ref, gx, f"grad_x (call {call})")
     if spmv_ops.spmv_kernel == "auto":
-        from numml_b200 import _plan
-        state = _plan.get_plan(m, k, di, dp).extra["values_symmetric"]
-        assert state[1] is (values == "laplacian")
+        assert spmv_ops.values_symmetric_state(m, k, di, dp) is (values == "laplacian")
 
 
 def test_c2_cg_100_iterations(oracle, ops, poisson128):

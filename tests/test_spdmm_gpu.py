@@ -9,10 +9,13 @@ from numml_b200 import workloads as W
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def ops():
+@pytest.fixture(params=["compiled shim", "python shim"])
+def ops(request):
     from numml_b200 import numml_torch_cpp
-    return numml_torch_cpp
+    old = numml_torch_cpp.use_compiled_shim
+    numml_torch_cpp.use_compiled_shim = request.param == "compiled shim"
+    yield numml_torch_cpp
+    numml_torch_cpp.use_compiled_shim = old
 
 
 def test_golden_spdmm(golden_ops, ops):

@@ -10,15 +10,17 @@ from numml_b200 import workloads as W
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["auto", "stream"])
+@pytest.fixture(params=["auto", "stream", "auto, python shim"])
 def ops(request):
-    """The operator module, once with automatic kernel choice (TMA-pipelined kernels where the
-    pattern allows) and once forced onto the register-staged streaming kernels."""
+    """The operator module, with automatic kernel choice (TMA-pipelined kernels where the pattern
+    allows) through the compiled shim and through the Python one, and forced onto the register-staged
+    streaming kernels."""
     from numml_b200 import numml_torch_cpp, _plan
-    old = numml_torch_cpp.spmv_kernel
-    numml_torch_cpp.spmv_kernel = request.param
+    old = (numml_torch_cpp.spmv_kernel, numml_torch_cpp.use_compiled_shim)
+    numml_torch_cpp.spmv_kernel = request.param.split(",")[0]
+    numml_torch_cpp.use_compiled_shim = "python" not in request.param
     yield numml_torch_cpp
-    numml_torch_cpp.spmv_kernel = old
+    numml_torch_cpp.spmv_kernel, numml_torch_cpp.use_compiled_shim = old
     numml_torch_cpp.check_status()
 
 
@@ -289,26 +291,30 @@ def test_row_range_entry_points(oracle):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("compiled", [True, False])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
-def test_value_symmetric_backward_is_chosen_only_when_it_applies(oracle, dtype):
+def test_value_symmetric_backward_is_chosen_only_when_it_applies(oracle, dtype, compiled):
     """The operator switches to the value-symmetric pass on the second call with unchanged values, and
     only if the device-side test finds the matrix equal to its transpose bit for bit; an in-place
     change of one value (version bump) sends it back to the general pass.  Results are bit-exact
     against the oracle in every state."""
-    from numml_b200 import numml_torch_cpp as ops, _plan
+    from numml_b200 import numml_torch_cpp as ops
+    old_shim = ops.use_compiled_shim
+    ops.use_compiled_shim = compiled
+    if compiled and ops.compiled_shim() is None:
+        ops.use_compiled_shim = old_shim
+        pytest.skip("the compiled shim has not been built")
     gen = W.poisson2d_5pt if dtype == torch.float32 else W.poisson3d_7pt
     d, i, p, (m, k) = gen(48 if dtype == torch.float32 else 24, dtype)
     x, g = W.randn(k, 0, dtype), W.randn(m, 1, dtype)
     dd, di, dp, dx, dg = [t.cuda() for t in (d, i, p, x, g)]
-    plan = _plan.get_plan(m, k, di, dp)
 
     def check(vals_cpu, vals_dev, expect_symmetric):
         gA_ref, gx_ref = oracle.spgemv_backward(g, m, k, vals_cpu, i, p, x)
         gA, gx = ops.spgemv_backward(dg, m, k, vals_dev, di, dp, dx)
         assert_same(gA_ref, gA, "grad_A")
         assert_same(gx_ref, gx, "grad_x")
-        state = plan.extra["values_symmetric"]
-        assert state[1] is expect_symmetric, state[:2]
+        assert ops.values_symmetric_state(m, k, di, dp) is expect_symmetric
 
     check(d, dd, None)            # first sighting of these values: general pass, nothing tested yet
     check(d, dd, True)            # second sighting: tested, symmetric -> value-symmetric pass from now on
@@ -320,3 +326,4 @@ def test_value_symmetric_backward_is_chosen_only_when_it_applies(oracle, dtype):
     check(d2, dd, False)          # tested, not symmetric: stays on the general pass
     check(d2, dd, False)
     ops.check_status()
+    ops.use_compiled_shim = old_shim
