@@ -217,34 +217,37 @@ NB200_API int nb200_spdmm_backward_grad_A(int64_t rows, int64_t cols, int64_t K,
  * cpp/sparse_csr_gemm_cuda.cu:223-302).
  *
  *   1. nb200_spgemm_plan      counts the products of every row of A, bins the rows and writes a
- *                             header of 16 int64 words at the start of `workspace`:
- *                             [0..4] rows per bin, [5] spill slots needed by the symbolic phase,
- *                             [6] largest product count of a row.
- *   2. nb200_spgemm_symbolic  counts the distinct columns of every row of C (rows with at most 32
- *                             products: one warp per row, no table; larger rows: per-bin hash tables
- *                             in shared memory; rows with more than 4096 products use `spill`, an
- *                             array of `spill_slots` uint32), writes C_indptr (int64, A_rows+1
- *                             entries) and extends the header: [8..12] rows per bin for the numeric
- *                             phase, [13] its spill slots, [14] nnz(C), [15] non-zero if a spill area
- *                             was too small (its rows are then skipped, nothing is written out of
- *                             bounds).
+ *                             header of 24 int64 words at the start of `workspace`:
+ *                             [0..5] rows per bin, [6] spill slots needed by the symbolic phase,
+ *                             [7] largest product count of a row.
+ *   2. nb200_spgemm_symbolic  counts the distinct columns of every row of C (rows whose row of A has at
+ *                             most 8 entries and 64 products: one thread per row merging the selected
+ *                             sorted rows of B; other rows with at most 32 products: one warp per row;
+ *                             larger rows: per-bin hash tables in shared memory; rows with more than
+ *                             4096 products use `spill`, an array of `spill_slots` uint32), writes
+ *                             C_indptr (int64, A_rows+1 entries) and extends the header: [8..13] rows
+ *                             per bin for the numeric phase, [14] its spill slots, [15] nnz(C),
+ *                             [16] non-zero if a spill area was too small (its rows are then skipped,
+ *                             nothing is written out of bounds).
  *   3. nb200_spgemm_numeric   fills C_indices (int64, ascending within a row) and C_data;
  *                             `spill` must hold spill_slots * (sizeof(value) + 4) bytes.
  *
- * The caller reads the header (a device-to-host copy of 128 bytes) after step 2 to size the outputs
+ * The caller reads the header (a device-to-host copy of 192 bytes) after step 2 to size the outputs
  * and the numeric spill area.  Steps 1 and 2 can be enqueued together with spill_slots = 0: only if
- * header[5] then turns out non-zero (a row with more than 4096 products exists) must both be repeated
+ * header[6] then turns out non-zero (a row with more than 4096 products exists) must both be repeated
  * with a spill area of that many slots.  C's pattern is purely structural: numerically cancelled
  * entries are stored as zeros, like the reference's.  C_indptr / C_indices are bit-identical to the
- * reference's.  Values of rows with at most 32 products (and at most 32 entries in the row of A) are
- * summed in the reference's order with unfused multiply and add: bit-identical to its CPU loop and
- * reproducible; values of larger rows are accumulated with atomics (order not fixed, within tolerance).
+ * reference's.  Values of the rows formed by one thread or one warp are summed in the reference's order
+ * with unfused multiply and add: bit-identical to its CPU loop and reproducible; values of larger rows
+ * are accumulated with atomics (order not fixed, within tolerance).  `B_rows_sorted` != 0 states that the
+ * columns of every row of B ascend strictly (nb200_csr_check), which the thread-per-row merge needs; with 0
+ * those rows take the warp or hash kernels instead and the result is the same.
  * `workspace` must hold nb200_spgemm_workspace_bytes(A_rows) bytes and be kept between the calls.
  * ------------------------------------------------------------------------------------------- */
 NB200_API size_t nb200_spgemm_workspace_bytes(int64_t A_rows);
 NB200_API int nb200_spgemm_plan(int64_t A_rows, int64_t A_cols, int64_t A_nnz,
-                                const void* A_indices, const void* A_indptr, const void* B_indptr, int itype,
-                                void* workspace, size_t workspace_bytes, nb200_stream stream);
+                                const void* A_indices, const void* A_indptr, const void* B_indptr, int B_rows_sorted,
+                                int itype, void* workspace, size_t workspace_bytes, nb200_stream stream);
 NB200_API int nb200_spgemm_symbolic(int64_t A_rows, int64_t A_cols, int64_t B_cols,
                                     const void* A_indices, const void* A_indptr,
                                     const void* B_indices, const void* B_indptr, int itype,

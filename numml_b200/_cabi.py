@@ -36,7 +36,7 @@ SIGNATURES = {
     "nb200_widen_indices": (_int, [_i64, _vp, _vp, _vp]),
     "nb200_spdmm_forward": (_int, [_i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
     "nb200_spgemm_workspace_bytes": (_sz, [_i64]),
-    "nb200_spgemm_plan": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _int, _vp, _sz, _vp]),
+    "nb200_spgemm_plan": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _int, _int, _vp, _sz, _vp]),
     "nb200_spgemm_symbolic": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp, _sz, _vp, _i64, _vp, _vp]),
     "nb200_spgemm_numeric": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp, _sz, _vp, _i64,
                                     _vp, _vp, _vp, _vp]),

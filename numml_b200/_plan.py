@@ -33,6 +33,13 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr() if t is not None and t.numel() > 0 else 0)
 
 
+def _published(device):
+    """Cached plan arrays are written once, on the stream that first needed them, and read for as long
+    as the pattern lives from whatever stream is current then.  Waiting once for the producing stream,
+    here, makes them safe to read from any stream afterwards."""
+    torch.cuda.current_stream(device).synchronize()
+
+
 class PatternPlan:
     def __init__(self, rows, cols, indices, indptr):
         self.rows, self.cols = int(rows), int(cols)
@@ -57,6 +64,7 @@ class PatternPlan:
                 p32 = torch.empty(self.rows + 1, dtype=torch.int32, device=self.indices.device)
                 _cabi.call("nb200_narrow_indices", self.nnz, _ptr(self.indices), _ptr(i32), _stream())
                 _cabi.call("nb200_narrow_indices", self.rows + 1, _ptr(self.indptr), _ptr(p32), _stream())
+                _published(self.indices.device)
             self._narrow = (i32, p32)
         return self._narrow[0], self._narrow[1], _cabi.I32
 
@@ -94,6 +102,7 @@ class PatternPlan:
         if self._t is None:
             idx, ptr, itype = self.csr()
             self._t = transpose_structure(self.rows, self.cols, idx, ptr, itype, itype) + (itype,)
+            _published(self.indices.device)
         return self._t
 
 
@@ -178,6 +187,7 @@ class PatternPlan:
                 lens = ptr[1:] - ptr[:-1]
                 if int(lens.max()) > 16 * max(1.0, self.nnz / rows):
                     order = torch.argsort(lens, descending=True, stable=True).to(torch.int32)
+                    _published(ptr.device)
             self.extra[key] = order
         return self.extra[key]
 

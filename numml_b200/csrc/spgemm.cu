@@ -2,21 +2,24 @@
 // and its masked backward, for CSR on sm_100a.
 //
 // Rows of C are binned by size (upper bound = number of products for the symbolic phase, exact
-// nnz for the numeric phase).  Bin 0 needs no table at all:
-//     bin 0:  one warp per row, no table                             (products <= 32, entries of A <= 32)
+// nnz for the numeric phase).  The first two bins need no table at all:
+//     bin 0:  one thread per row                                     (entries of A <= 8, products <= 64)
+//             the selected rows of B are sorted runs; the thread merges them in registers, which yields the
+//             columns in ascending order and the products of a column in run order -- the reference's order
+//             of additions.  A warp forms 32 rows for the instruction cost of one.
+//     bin 1:  one warp per row                                       (products <= 32, entries of A <= 32)
 //             lane p owns product p in the reference's accumulation order (entries of the row of A in
 //             storage order, for each the entries of the row of B in storage order); equal columns find
 //             each other with match.any, the lowest lane of a group is its leader, a leader's position in
 //             the sorted row is the number of leaders with a smaller column, and the group's products are
-//             added in lane order -- the reference's order, so these rows come out bit-identical to its
-//             CPU loop and the same from run to run.  The loads behind a row form a chain five levels deep;
-//             a warp keeps five rows in flight, one per level, so that the chain's latency is paid once per
-//             five rows.
+//             added in lane order.  The loads behind a row form a chain five levels deep; a warp keeps five
+//             rows in flight, one per level, so that the chain's latency is paid once per five rows.
+//     Rows of both bins come out bit-identical to the reference's CPU loop and the same from run to run.
 // The other bins have a team size and an open-addressing hash table:
-//     bin 1:   8 lanes per row,  64-slot table in shared memory      (size <= 32)
-//     bin 2:  32 lanes per row, 512-slot table in shared memory      (size <= 256)
-//     bin 3: 256 threads per row, 8192-slot (symbolic) / 4096-slot (numeric) table in shared memory
-//     bin 4: 256 threads per row, table in a caller-provided global-memory spill area
+//     bin 2:   8 lanes per row,  64-slot table in shared memory      (size <= 32)
+//     bin 3:  32 lanes per row, 512-slot table in shared memory      (size <= 256)
+//     bin 4: 256 threads per row, 8192-slot (symbolic) / 4096-slot (numeric) table in shared memory
+//     bin 5: 256 threads per row, table in a caller-provided global-memory spill area
 // Column keys are inserted with atomicCAS and linear probing (load factor <= 1/2); the numeric
 // phase accumulates values with shared/global atomics and then emits the row in ascending column
 // order: for 64-slot tables the occupied slots are gathered into a dense list and every entry is
@@ -35,25 +38,30 @@
 namespace nb200 {
 
 constexpr uint32_t kEmptyKey = 0xffffffffu;
-constexpr int kBins = 5;
-constexpr int kWarpRowMax = 32;    // products (and entries of A) a row may have to be formed by one warp
-constexpr int kHeaderWords = 16;   // int64 words at the start of the workspace
+constexpr int kBins = 6;
+constexpr int kThreadRowEntries = 8;   // entries of A a row may have to be merged by one thread ...
+constexpr int kThreadRowMax = 64;      // ... and products
+constexpr int kWarpRowMax = 32;        // products (and entries of A) a row may have to be formed by one warp
+constexpr int kSpillBin = 5;
+constexpr int kHeaderWords = 24;       // int64 words at the start of the workspace
 // header layout (int64):
-//   [0..4]  rows per bin, symbolic classification (by number of products)
-//   [5]     spill slots needed by the symbolic phase (bin 4 tables)
-//   [6]     largest per-row number of products
-//   [8..12] rows per bin, numeric classification (bin 0 by products, the others by nnz of the output row)
-//   [13]    spill slots needed by the numeric phase
-//   [14]    nnz(C)
-//   [15]    error word (non-zero: a spill table was too small)
-constexpr int kHdrSymSpill = 5, kHdrMaxProducts = 6, kHdrNumBins = 8, kHdrNumSpill = 13, kHdrNnz = 14, kHdrError = 15;
+//   [0..5]  rows per bin, symbolic classification
+//   [6]     spill slots needed by the symbolic phase (tables of the last bin)
+//   [7]     largest per-row number of products
+//   [8..13] rows per bin, numeric classification (bins 0 and 1 as in the symbolic phase, the others by nnz
+//           of the output row)
+//   [14]    spill slots needed by the numeric phase
+//   [15]    nnz(C)
+//   [16]    error word (non-zero: a spill table was too small)
+constexpr int kHdrSymSpill = 6, kHdrMaxProducts = 7, kHdrNumBins = 8, kHdrNumSpill = 14, kHdrNnz = 15, kHdrError = 16;
+enum RowKind : unsigned char { kThreadRow = 0, kWarpRow = 1, kHashRow = 2 };
 
-// hash bins 1..4 by table size needed
+// hash bins 2..5 by table size needed
 __host__ __device__ inline int hash_bin_of(int64_t size, bool numeric) {
-    if (size <= 32) return 1;
-    if (size <= 256) return 2;
-    if (size <= (numeric ? 2048 : 4096)) return 3;
-    return 4;
+    if (size <= 32) return 2;
+    if (size <= 256) return 3;
+    if (size <= (numeric ? 2048 : 4096)) return 4;
+    return 5;
 }
 
 __device__ __forceinline__ int64_t spill_table_size(int64_t size) {
@@ -80,6 +88,7 @@ __device__ __forceinline__ uint32_t table_insert(uint32_t* keys, uint32_t mask, 
 template <typename I>
 __global__ void spgemm_products_kernel(int64_t rows, const I* __restrict__ A_indices, const I* __restrict__ A_indptr,
                                        const I* __restrict__ B_indptr, int32_t* __restrict__ size_out,
+                                       unsigned char* __restrict__ kind_out, bool b_sorted,
                                        unsigned long long* __restrict__ header) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     long long local_max = 0;
@@ -89,9 +98,13 @@ __global__ void spgemm_products_kernel(int64_t rows, const I* __restrict__ A_ind
             const int64_t j = (int64_t)A_indices[a];
             ub += (long long)B_indptr[j + 1] - (long long)B_indptr[j];
         }
-        // a row takes the warp path only if its entries of A fit one warp too; folding their number into
-        // the size keeps one array (a larger size only means a larger table)
-        ub = max(ub, (long long)A_indptr[r + 1] - (long long)A_indptr[r]);
+        // which kernel forms the row: a thread merging a few sorted runs, a warp with one product per lane,
+        // or a hash table.  For the last the number of entries of A is folded into the size (a larger size
+        // only means a larger table).
+        const long long na = (long long)A_indptr[r + 1] - (long long)A_indptr[r];
+        kind_out[r] = (b_sorted && na <= kThreadRowEntries && ub <= kThreadRowMax) ? kThreadRow
+                      : (na <= kWarpRowMax && ub <= kWarpRowMax) ? kWarpRow : kHashRow;
+        ub = max(ub, na);
         if (ub > 0x7fffffffLL) ub = 0x7fffffffLL;
         size_out[r] = (int32_t)ub;
         local_max = max(local_max, ub);
@@ -102,11 +115,11 @@ __global__ void spgemm_products_kernel(int64_t rows, const I* __restrict__ A_ind
 }
 
 // Distribute rows into per-bin lists (warp-aggregated appends) and size the spill tables.
-// `products` is the array written by spgemm_products_kernel; `size_in` is that array again (symbolic
-// phase) or the exact nnz of every output row (numeric phase).
+// `kind` is written by spgemm_products_kernel; `size_in` is its product counts (symbolic phase) or the
+// exact nnz of every output row (numeric phase).
 __global__ void __launch_bounds__(256)
 spgemm_classify_kernel(int64_t rows, const int32_t* __restrict__ size_in,
-                       const int32_t* __restrict__ products, bool numeric,
+                       const unsigned char* __restrict__ kind, bool numeric,
                        int32_t* __restrict__ lists, int64_t* __restrict__ spill_off,
                        unsigned long long* __restrict__ header) {
     // appends are aggregated per warp (match.any), then per block (shared counters): one global atomic
@@ -123,7 +136,7 @@ spgemm_classify_kernel(int64_t rows, const int32_t* __restrict__ size_in,
         const bool ok = r < rows;
         const int32_t size = ok ? size_in[r] : 0;
         int bin = kBins;
-        if (ok) bin = products[r] <= kWarpRowMax ? 0 : hash_bin_of(size, numeric);
+        if (ok) bin = kind[r] != kHashRow ? (int)kind[r] : hash_bin_of(size, numeric);
         const uint32_t peers = __match_any_sync(0xffffffffu, bin);
         const int leader = __ffs(peers) - 1;
         unsigned warp_off = 0;
@@ -136,15 +149,80 @@ spgemm_classify_kernel(int64_t rows, const int32_t* __restrict__ size_in,
         if (ok) {
             const int64_t pos = (int64_t)s_base[bin] + warp_off + __popc(peers & ((1u << lane) - 1u));
             lists[(int64_t)bin * rows + pos] = (int32_t)r;
-            if (bin == 4) spill_off[pos] = (int64_t)atomicAdd(header + hb + kHdrSymSpill, (unsigned long long)spill_table_size(size));
+            if (bin == kSpillBin) spill_off[pos] = (int64_t)atomicAdd(header + hb + kHdrSymSpill, (unsigned long long)spill_table_size(size));
         }
         __syncthreads();
     }
 }
 
 // ---------------------------------------------------------------------------------------------
-// Bin 0: one warp per row, no table.
+// Bins 0 and 1: rows formed without a table.
 // ---------------------------------------------------------------------------------------------
+// ---------------------------------------------------------------------------------------------
+// Bin 0: one thread per row.  The rows of B that a row of A selects are sorted runs; with at most
+// kThreadRowEntries of them a thread keeps every run's position, end and head column in registers and
+// merges them: the smallest head column is the next column of the output row, and the runs whose head
+// equals it contribute their products in run order -- the reference's order of additions, so the values
+// are bit-identical to its CPU loop -- before they advance.  No table, no sort, no shuffles; a warp
+// forms 32 rows at the instruction cost of one, and neighbouring threads read neighbouring rows.
+// ---------------------------------------------------------------------------------------------
+template <typename T, typename I, bool NUMERIC>
+__global__ void __launch_bounds__(256)
+spgemm_thread_rows_kernel(const int32_t* __restrict__ list, const unsigned long long* __restrict__ count_ptr,
+                          const T* __restrict__ A_data, const I* __restrict__ A_indices, const I* __restrict__ A_indptr,
+                          const T* __restrict__ B_data, const I* __restrict__ B_indices, const I* __restrict__ B_indptr,
+                          int32_t* __restrict__ row_nnz, const int64_t* __restrict__ C_indptr,
+                          int64_t* __restrict__ C_indices, T* __restrict__ C_data) {
+    constexpr int E = kThreadRowEntries;
+    const int64_t count = (int64_t)*count_ptr;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < count; idx += stride) {
+        const int64_t row = (int64_t)list[idx];
+        const int64_t a0 = (int64_t)A_indptr[row];
+        const int na = (int)((int64_t)A_indptr[row + 1] - a0);
+        I pos[E], end[E];
+        uint32_t head[E];
+        T av[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            pos[e] = 0; end[e] = 0; head[e] = kEmptyKey; av[e] = (T)0;
+            if (e < na) {
+                const int64_t j = (int64_t)A_indices[a0 + e];
+                pos[e] = B_indptr[j];
+                end[e] = B_indptr[j + 1];
+                if (NUMERIC) av[e] = A_data[a0 + e];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+            if (pos[e] < end[e]) head[e] = (uint32_t)B_indices[pos[e]];
+        int64_t out = 0;
+        if (NUMERIC) out = C_indptr[row];
+        int n = 0;
+        while (true) {
+            uint32_t next = kEmptyKey;
+#pragma unroll
+            for (int e = 0; e < E; ++e) next = min(next, head[e]);
+            if (next == kEmptyKey) break;
+            T sum = (T)0;
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                if (head[e] == next) {
+                    if (NUMERIC) sum = add_rn(sum, mul_rn(av[e], B_data[pos[e]]));
+                    ++pos[e];
+                    head[e] = pos[e] < end[e] ? (uint32_t)B_indices[pos[e]] : kEmptyKey;
+                }
+            }
+            if (NUMERIC) {
+                C_indices[out + n] = (int64_t)next;
+                C_data[out + n] = sum;
+            }
+            ++n;
+        }
+        if (!NUMERIC) row_nnz[row] = n;
+    }
+}
+
 // The kernel is bound by the chain of dependent loads behind every row (row list -> row pointers of A
 // -> entries of A -> row pointers of B -> entries of B), not by arithmetic, so the chain is software-
 // pipelined five rows deep: in every iteration a warp issues one load level for each of the five rows
@@ -533,6 +611,7 @@ struct SpgemmWorkspace {
     int32_t* row_nnz;
     int32_t* lists;      // kBins x rows
     int64_t* spill_off;  // rows
+    unsigned char* kind; // rows
     char* scan;
     size_t scan_bytes;
     bool ok;
@@ -541,7 +620,7 @@ struct SpgemmWorkspace {
 static size_t spgemm_workspace_bytes(int64_t rows) {
     const size_t r = (size_t)(rows > 0 ? rows : 1);
     return Workspace::pad(kHeaderWords * sizeof(int64_t)) + 2 * Workspace::pad(r * sizeof(int32_t)) +
-           Workspace::pad(kBins * r * sizeof(int32_t)) + Workspace::pad(r * sizeof(int64_t)) +
+           Workspace::pad(kBins * r * sizeof(int32_t)) + Workspace::pad(r * sizeof(int64_t)) + Workspace::pad(r) +
            Workspace::pad(scan_scratch_bytes(rows));
 }
 
@@ -554,6 +633,7 @@ static SpgemmWorkspace carve(int64_t rows, void* workspace, size_t bytes) {
     w.row_nnz = ws.take<int32_t>(r);
     w.lists = ws.take<int32_t>(kBins * r);
     w.spill_off = ws.take<int64_t>(r);
+    w.kind = ws.take<unsigned char>(r);
     w.scan_bytes = scan_scratch_bytes(rows);
     w.scan = ws.take<char>(w.scan_bytes);
     w.ok = ws.ok();
@@ -568,14 +648,14 @@ static inline unsigned flat_grid(int64_t n) {
 }
 
 template <typename I>
-int spgemm_plan(int64_t A_rows, const I* A_indices, const I* A_indptr, const I* B_indptr,
+int spgemm_plan(int64_t A_rows, const I* A_indices, const I* A_indptr, const I* B_indptr, bool b_sorted,
                 void* workspace, size_t bytes, cudaStream_t st) {
     SpgemmWorkspace w = carve(A_rows, workspace, bytes);
     if (!w.ok) return NB200_ERR_WORKSPACE;
     if (cudaMemsetAsync(w.header, 0, kHeaderWords * sizeof(int64_t), st) != cudaSuccess) return NB200_ERR_CUDA;
     if (A_rows == 0) return NB200_OK;
-    spgemm_products_kernel<I><<<flat_grid(A_rows), 256, 0, st>>>(A_rows, A_indices, A_indptr, B_indptr, w.size, w.header);
-    spgemm_classify_kernel<<<flat_grid(A_rows), 256, 0, st>>>(A_rows, w.size, w.size, false, w.lists, w.spill_off, w.header);
+    spgemm_products_kernel<I><<<flat_grid(A_rows), 256, 0, st>>>(A_rows, A_indices, A_indptr, B_indptr, w.size, w.kind, b_sorted, w.header);
+    spgemm_classify_kernel<<<flat_grid(A_rows), 256, 0, st>>>(A_rows, w.size, w.kind, false, w.lists, w.spill_off, w.header);
     return launch_status();
 }
 
@@ -587,23 +667,25 @@ int spgemm_symbolic(int64_t A_rows, const I* A_indices, const I* A_indptr, const
     if (!w.ok) return NB200_ERR_WORKSPACE;
     if (A_rows > 0) {
         const unsigned g = persistent_grid();
-        spgemm_warp_rows_kernel<double, I, false><<<persistent_grid(kWarpRowsCtasPerSm), 256, 0, st>>>(
+        spgemm_thread_rows_kernel<double, I, false><<<persistent_grid(), 256, 0, st>>>(
             w.lists, w.header + 0, nullptr, A_indices, A_indptr, nullptr, B_indices, B_indptr, w.row_nnz, nullptr, nullptr, nullptr);
+        spgemm_warp_rows_kernel<double, I, false><<<persistent_grid(kWarpRowsCtasPerSm), 256, 0, st>>>(
+            w.lists + A_rows, w.header + 1, nullptr, A_indices, A_indptr, nullptr, B_indices, B_indptr, w.row_nnz, nullptr, nullptr, nullptr);
 #define NB200_SYM(TEAM, SUB, TLOG, SPILL, BIN)                                                              \
         spgemm_symbolic_kernel<I, TEAM, SUB, TLOG, SPILL><<<g, 256, 0, st>>>(                                 \
             w.lists + (int64_t)(BIN) * A_rows, w.header + (BIN), A_indices, A_indptr, B_indices, B_indptr,  \
             w.size, w.spill_off, spill, spill_slots, w.header, w.row_nnz)
-        NB200_SYM(8, 1, 6, false, 1);
-        NB200_SYM(32, 4, 9, false, 2);
-        NB200_SYM(256, 32, 13, false, 3);
-        NB200_SYM(256, 32, 0, true, 4);
+        NB200_SYM(8, 1, 6, false, 2);
+        NB200_SYM(32, 4, 9, false, 3);
+        NB200_SYM(256, 32, 13, false, 4);
+        NB200_SYM(256, 32, 0, true, 5);
 #undef NB200_SYM
     }
     int rc = exclusive_scan_i32_to_i64(A_rows, w.row_nnz, C_indptr, w.scan, w.scan_bytes, st);
     if (rc != NB200_OK) return rc;
     if (A_rows > 0) {
         // numeric classification by exact row size; nnz(C) goes to header[13]
-        spgemm_classify_kernel<<<flat_grid(A_rows), 256, 0, st>>>(A_rows, w.row_nnz, w.size, true, w.lists, w.spill_off, w.header);
+        spgemm_classify_kernel<<<flat_grid(A_rows), 256, 0, st>>>(A_rows, w.row_nnz, w.kind, true, w.lists, w.spill_off, w.header);
     }
     if (cudaMemcpyAsync(w.header + kHdrNnz, C_indptr + A_rows, sizeof(int64_t), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
         return NB200_ERR_CUDA;
@@ -622,16 +704,18 @@ int spgemm_numeric(int64_t A_rows, const T* A_data, const I* A_indices, const I*
     T* spill_vals = static_cast<T*>(spill);
     uint32_t* spill_keys = reinterpret_cast<uint32_t*>(spill_vals + (spill_slots > 0 ? spill_slots : 0));
     const unsigned g = persistent_grid();
-    spgemm_warp_rows_kernel<T, I, true><<<persistent_grid(kWarpRowsCtasPerSm), 256, 0, st>>>(
+    spgemm_thread_rows_kernel<T, I, true><<<persistent_grid(), 256, 0, st>>>(
         w.lists, w.header + kHdrNumBins, A_data, A_indices, A_indptr, B_data, B_indices, B_indptr, nullptr, C_indptr, C_indices, C_data);
+    spgemm_warp_rows_kernel<T, I, true><<<persistent_grid(kWarpRowsCtasPerSm), 256, 0, st>>>(
+        w.lists + A_rows, w.header + kHdrNumBins + 1, A_data, A_indices, A_indptr, B_data, B_indices, B_indptr, nullptr, C_indptr, C_indices, C_data);
 #define NB200_NUM(TEAM, SUB, TLOG, SPILL, BIN)                                                                   \
     spgemm_numeric_kernel<T, I, TEAM, SUB, TLOG, SPILL><<<g, 256, 0, st>>>(                                       \
         w.lists + (int64_t)(BIN) * A_rows, w.header + kHdrNumBins + (BIN), A_data, A_indices, A_indptr, B_data, B_indices, \
         B_indptr, w.row_nnz, w.spill_off, spill_keys, spill_vals, spill_slots, w.header, C_indptr, C_indices, C_data)
-    NB200_NUM(8, 1, 6, false, 1);
-    NB200_NUM(32, 4, 9, false, 2);
-    NB200_NUM(256, 32, 12, false, 3);
-    NB200_NUM(256, 32, 0, true, 4);
+    NB200_NUM(8, 1, 6, false, 2);
+    NB200_NUM(32, 4, 9, false, 3);
+    NB200_NUM(256, 32, 12, false, 4);
+    NB200_NUM(256, 32, 0, true, 5);
 #undef NB200_NUM
     return launch_status();
 }
@@ -643,15 +727,15 @@ using namespace nb200;
 extern "C" size_t nb200_spgemm_workspace_bytes(int64_t A_rows) { return spgemm_workspace_bytes(A_rows); }
 
 extern "C" int nb200_spgemm_plan(int64_t A_rows, int64_t A_cols, int64_t A_nnz,
-                                 const void* A_indices, const void* A_indptr, const void* B_indptr, int itype,
-                                 void* workspace, size_t workspace_bytes, nb200_stream stream) {
+                                 const void* A_indices, const void* A_indptr, const void* B_indptr, int B_rows_sorted,
+                                 int itype, void* workspace, size_t workspace_bytes, nb200_stream stream) {
     (void)A_cols;
     if (A_rows < 0 || A_nnz < 0 || !workspace) return NB200_ERR_BAD_ARG;
     if (A_rows >= 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
     if (A_rows > 0 && (!A_indptr || !B_indptr || (A_nnz > 0 && !A_indices))) return NB200_ERR_BAD_ARG;
     return NB200_DISPATCH_I(itype,
-        (spgemm_plan<I>(A_rows, (const I*)A_indices, (const I*)A_indptr, (const I*)B_indptr, workspace, workspace_bytes,
-                        as_stream(stream))));
+        (spgemm_plan<I>(A_rows, (const I*)A_indices, (const I*)A_indptr, (const I*)B_indptr, B_rows_sorted != 0, workspace,
+                        workspace_bytes, as_stream(stream))));
 }
 
 extern "C" int nb200_spgemm_symbolic(int64_t A_rows, int64_t A_cols, int64_t B_cols,

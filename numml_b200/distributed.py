@@ -622,7 +622,7 @@ class DistSpMVEngine:
             if peer.usable:
                 self.peer = peer
                 self.exchange = "peer memory: neighbours' packed values read over NVLink by this library's kernels, step flags with bounded waits"
-                self.schedule = ("publish -> [pull -> boundary rows || interior rows]; [ghost rows -> publish || local rows] -> pull-add"
+                self.schedule = ("[publish -> pull -> boundary rows || interior rows]; [ghost rows -> publish || local rows] -> pull-add"
                                  " (two streams, no communication library in the step)")
                 self.launches_per_step = 4 + 4
             elif self._exchange_request == "peer":
@@ -754,14 +754,14 @@ class DistSpMVEngine:
         lib = self._lib
         stream = self._c.c_void_p(torch.cuda.current_stream().cuda_stream)
         if self.peer is not None:
-            # the small kernels (pull, boundary rows) go to a side stream and are issued first, so that they
-            # take their few SMs at once and run under the cover of the interior rows
+            # the small kernels (publish, pull, boundary rows) go to a side stream and are issued first, so that
+            # they take their few SMs at once and run under the cover of the interior rows, which need none of them
             main = torch.cuda.current_stream()
             side = self._side_stream()
-            self._launch(lib.nb200_halo_publish, self._peer_publish_x, stream)
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 s2 = self._c.c_void_p(side.cuda_stream)
+                self._launch(lib.nb200_halo_publish, self._peer_publish_x, s2)
                 self._launch(lib.nb200_halo_pull, self._peer_pull_x, s2)
                 for args in self._fwd_boundary:
                     self._launch(lib.nb200_spgemv_forward, args, s2)

@@ -315,13 +315,13 @@ def _common_width(plan_a, plan_b):
     return plan_a.indices, plan_a.indptr, plan_b.indices, plan_b.indptr, _cabi.I64
 
 
-# positions in the 16-word header of an SpGEMM workspace (see nb200_spgemm_plan in the C header)
-_HDR_SYM_SPILL, _HDR_NUM_SPILL, _HDR_NNZ, _HDR_ERROR = 5, 13, 14, 15
+# positions in the 24-word header of an SpGEMM workspace (see nb200_spgemm_plan in the C header)
+_HDR_SYM_SPILL, _HDR_NUM_SPILL, _HDR_NNZ, _HDR_ERROR = 6, 14, 15, 16
 
 
 def _header(work):
-    """The 16-word int64 header at the start of an SpGEMM workspace (device-to-host copy, syncs)."""
-    return work[:128].view(torch.int64).cpu()
+    """The 24-word int64 header at the start of an SpGEMM workspace (device-to-host copy, syncs)."""
+    return work[:192].view(torch.int64).cpu()
 
 
 def spgemm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B_rows, B_cols, B_data, B_indices, B_indptr):
@@ -338,8 +338,10 @@ def spgemm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B_rows, B_cols, 
         work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
         C_indptr = torch.empty(A_rows + 1, dtype=torch.int64, device=dev)
 
+        b_sorted = int(not (plan_b.check_flags() & _plan.CHECK_UNSORTED))
+
         def count(spill, slots):
-            _cabi.call("nb200_spgemm_plan", A_rows, A_cols, plan_a.nnz, _ptr(ai), _ptr(ap), _ptr(bp), itype,
+            _cabi.call("nb200_spgemm_plan", A_rows, A_cols, plan_a.nnz, _ptr(ai), _ptr(ap), _ptr(bp), b_sorted, itype,
                        _ptr(work), wbytes, _stream())
             _cabi.call("nb200_spgemm_symbolic", A_rows, A_cols, B_cols, _ptr(ai), _ptr(ap), _ptr(bi), _ptr(bp), itype,
                        _ptr(work), wbytes, _ptr(spill), slots, _ptr(C_indptr), _stream())

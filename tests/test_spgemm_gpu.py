@@ -101,6 +101,27 @@ def test_small_rows_are_bit_exact(oracle, ops, dtype):
     assert_same(Cd_ref[small], Cd.cpu()[small], "values of the rows formed by one warp")
 
 
+def test_unsorted_right_factor_still_multiplies(oracle, ops):
+    """The thread-per-row merge needs the rows of B sorted; with unsorted rows those rows of C are formed
+    by the warp or hash kernels instead and the product is the same (structure exact, values at tolerance,
+    as the order of additions within a column then follows B's storage order)."""
+    import numpy as np
+    A = W.random_csr(400, 300, 0.01, seed=41, dtype=torch.float64)
+    bd, bi, bp, (bm, bn) = W.random_csr(300, 200, 0.03, seed=42, dtype=torch.float64)
+    rng = np.random.default_rng(0)
+    bd, bi = bd.clone(), bi.clone()
+    for r in range(bm):                                   # reverse the entries of every second row
+        if r % 2 == 0:
+            a, b = int(bp[r]), int(bp[r + 1])
+            bd[a:b], bi[a:b] = bd[a:b].flip(0), bi[a:b].flip(0)
+    B = (bd, bi, bp, (bm, bn))
+    ref = oracle.spgemm_forward(400, 300, *A[:3], bm, bn, bd, bi, bp)
+    (Cd, Ci, Cp), _ = run_case(ops, A, B)
+    assert_same(ref[2], Cp, "C_indptr")
+    assert_same(ref[1], Ci, "C_indices")
+    assert_close(ref[0], Cd, "C_data")
+
+
 def test_empty_operands(ops):
     z = (torch.zeros(0, dtype=torch.float64), torch.zeros(0, dtype=torch.int64), torch.zeros(5, dtype=torch.int64), (4, 3))
     B = W.random_csr(3, 6, 0.5, seed=1, dtype=torch.float64, empty_rows=False)
