@@ -166,6 +166,8 @@ spgemm_classify_kernel(int64_t rows, const int32_t* __restrict__ size_in,
 // are bit-identical to its CPU loop -- before they advance.  No table, no sort, no shuffles; a warp
 // forms 32 rows at the instruction cost of one, and neighbouring threads read neighbouring rows.
 // ---------------------------------------------------------------------------------------------
+constexpr int kThreadRowStage = 448;   // output entries of one warp's 32 rows that fit its staging area
+
 template <typename T, typename I, bool NUMERIC>
 __global__ void __launch_bounds__(256)
 spgemm_thread_rows_kernel(const int32_t* __restrict__ list, const unsigned long long* __restrict__ count_ptr,
@@ -174,12 +176,25 @@ spgemm_thread_rows_kernel(const int32_t* __restrict__ list, const unsigned long 
                           int32_t* __restrict__ row_nnz, const int64_t* __restrict__ C_indptr,
                           int64_t* __restrict__ C_indices, T* __restrict__ C_data) {
     constexpr int E = kThreadRowEntries;
+    constexpr unsigned kAll = 0xffffffffu;
+    // numeric phase: the rows of a warp are usually 32 consecutive rows of C, i.e. one contiguous range of
+    // C_indices / C_data.  The threads then write their rows into a staging area of the warp and the warp
+    // copies the range out with 16-byte stores, instead of 32 threads storing 8 bytes each at a row's stride.
+    __shared__ uint32_t s_col[NUMERIC ? 8 * kThreadRowStage : 1];
+    __shared__ T s_val[NUMERIC ? 8 * kThreadRowStage : 1];
+    const int lane = threadIdx.x & 31;
     const int64_t count = (int64_t)*count_ptr;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < count; idx += stride) {
-        const int64_t row = (int64_t)list[idx];
-        const int64_t a0 = (int64_t)A_indptr[row];
-        const int na = (int)((int64_t)A_indptr[row + 1] - a0);
+    for (int64_t base = (int64_t)blockIdx.x * blockDim.x + (threadIdx.x & ~31); base < count; base += stride) {
+        const int64_t idx = base + lane;
+        const bool active = idx < count;
+        const int64_t row = active ? (int64_t)list[idx] : -1;
+        int64_t a0 = 0;
+        int na = 0;
+        if (active) {
+            a0 = (int64_t)A_indptr[row];
+            na = (int)((int64_t)A_indptr[row + 1] - a0);
+        }
         I pos[E], end[E];
         uint32_t head[E];
         T av[E];
@@ -197,7 +212,22 @@ spgemm_thread_rows_kernel(const int32_t* __restrict__ list, const unsigned long 
         for (int e = 0; e < E; ++e)
             if (pos[e] < end[e]) head[e] = (uint32_t)B_indices[pos[e]];
         int64_t out = 0;
-        if (NUMERIC) out = C_indptr[row];
+        bool staged = false;
+        int64_t warp_out = 0;
+        int warp_total = 0;
+        uint32_t* wcol = s_col + (threadIdx.x >> 5) * kThreadRowStage;
+        T* wval = s_val + (threadIdx.x >> 5) * kThreadRowStage;
+        if (NUMERIC) {
+            if (active) out = C_indptr[row];
+            const int64_t row0 = __shfl_sync(kAll, row, 0);
+            warp_out = __shfl_sync(kAll, out, 0);
+            if (__all_sync(kAll, active && row == row0 + lane)) {
+                const int64_t total = C_indptr[row0 + 32] - warp_out;
+                staged = total <= kThreadRowStage;
+                warp_total = (int)total;
+            }
+        }
+        const int off = (int)(out - warp_out);
         int n = 0;
         while (true) {
             uint32_t next = kEmptyKey;
@@ -214,12 +244,42 @@ spgemm_thread_rows_kernel(const int32_t* __restrict__ list, const unsigned long 
                 }
             }
             if (NUMERIC) {
-                C_indices[out + n] = (int64_t)next;
-                C_data[out + n] = sum;
+                if (staged) { wcol[off + n] = next; wval[off + n] = sum; }
+                else { C_indices[out + n] = (int64_t)next; C_data[out + n] = sum; }
             }
             ++n;
         }
-        if (!NUMERIC) row_nnz[row] = n;
+        if (!NUMERIC && active) row_nnz[row] = n;
+        if (NUMERIC && staged) {
+            __syncwarp();
+            constexpr int V = 16 / (int)sizeof(T);                    // values per 16 bytes
+            // columns: two int64 per 16-byte store where the address allows; values likewise
+            const int head_c = (int)(warp_out & 1);                  // entries before the first 16-byte boundary of C_indices
+            if (lane < head_c && lane < warp_total) C_indices[warp_out + lane] = (int64_t)wcol[lane];
+            for (int q = head_c + 2 * lane; q < warp_total; q += 64) {
+                if (q + 1 < warp_total) {
+                    longlong2 two;
+                    two.x = (long long)wcol[q];
+                    two.y = (long long)wcol[q + 1];
+                    *reinterpret_cast<longlong2*>(C_indices + warp_out + q) = two;
+                } else {
+                    C_indices[warp_out + q] = (int64_t)wcol[q];
+                }
+            }
+            const int head_v = (int)((V - (warp_out & (V - 1))) & (V - 1));
+            if (lane < head_v && lane < warp_total) C_data[warp_out + lane] = wval[lane];
+            for (int q = head_v + V * lane; q < warp_total; q += 32 * V) {
+                if (q + V <= warp_total) {
+                    alignas(16) T tmp[V];
+#pragma unroll
+                    for (int t = 0; t < V; ++t) tmp[t] = wval[q + t];
+                    *reinterpret_cast<int4*>(C_data + warp_out + q) = *reinterpret_cast<const int4*>(tmp);
+                } else {
+                    for (int t = 0; q + t < warp_total; ++t) C_data[warp_out + q + t] = wval[q + t];
+                }
+            }
+            __syncwarp();
+        }
     }
 }
 
@@ -667,7 +727,7 @@ int spgemm_symbolic(int64_t A_rows, const I* A_indices, const I* A_indptr, const
     if (!w.ok) return NB200_ERR_WORKSPACE;
     if (A_rows > 0) {
         const unsigned g = persistent_grid();
-        spgemm_thread_rows_kernel<double, I, false><<<persistent_grid(), 256, 0, st>>>(
+        spgemm_thread_rows_kernel<double, I, false><<<persistent_grid(5), 256, 0, st>>>(
             w.lists, w.header + 0, nullptr, A_indices, A_indptr, nullptr, B_indices, B_indptr, w.row_nnz, nullptr, nullptr, nullptr);
         spgemm_warp_rows_kernel<double, I, false><<<persistent_grid(kWarpRowsCtasPerSm), 256, 0, st>>>(
             w.lists + A_rows, w.header + 1, nullptr, A_indices, A_indptr, nullptr, B_indices, B_indptr, w.row_nnz, nullptr, nullptr, nullptr);
@@ -704,7 +764,7 @@ int spgemm_numeric(int64_t A_rows, const T* A_data, const I* A_indices, const I*
     T* spill_vals = static_cast<T*>(spill);
     uint32_t* spill_keys = reinterpret_cast<uint32_t*>(spill_vals + (spill_slots > 0 ? spill_slots : 0));
     const unsigned g = persistent_grid();
-    spgemm_thread_rows_kernel<T, I, true><<<persistent_grid(), 256, 0, st>>>(
+    spgemm_thread_rows_kernel<T, I, true><<<persistent_grid(4), 256, 0, st>>>(
         w.lists, w.header + kHdrNumBins, A_data, A_indices, A_indptr, B_data, B_indices, B_indptr, nullptr, C_indptr, C_indices, C_data);
     spgemm_warp_rows_kernel<T, I, true><<<persistent_grid(kWarpRowsCtasPerSm), 256, 0, st>>>(
         w.lists + A_rows, w.header + kHdrNumBins + 1, A_data, A_indices, A_indptr, B_data, B_indices, B_indptr, nullptr, C_indptr, C_indices, C_data);
