@@ -332,6 +332,53 @@ NB200_API int nb200_masked_outer(int64_t rows, int64_t nnz, int64_t nrhs, const 
                                  int dtype, int itype, nb200_stream stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Triangular solve for narrow dependency levels, inside one thread-block cluster.  Same operator and
+ * same results (bit for bit) as nb200_sptrsv_solve; no counterpart of its own in the reference, whose
+ * CUDA solve is one kernel (cpp/sparse_csr_cuda.cu:714-831).
+ *
+ * For factors with thousands of levels of a few hundred rows (banded and stencil factors in natural
+ * ordering) the grid-wide solve pays one round trip through L2 per level.  Here one cluster of
+ * `cluster_ctas` CTAs (1, 2, 4, 8 or 16; 0 = 8) takes the levels one after the other, a team of lanes
+ * per row and a lane per right-hand side, keeps the unknowns of the most recent rows in a ring spread
+ * over the shared memory of its CTAs, reads dependencies from there through distributed shared memory,
+ * and separates levels by the hardware cluster barrier.  No thread waits on a flag.
+ *
+ * nb200_sptrsv_analyse_levels   nb200_sptrsv_analyse that also writes `level_ptr` (capacity n + 1 int32;
+ *                               nlevels + 1 are written): the first position in `order` of every level.
+ * nb200_sptrsv_level_plan       once per pattern, triangle and (for the transposed system) permutation:
+ *                               the structure in position order (position p = row order[p]):
+ *                               `pos_ptr` (n + 1 int32), and per kept entry -- those on the solve side of
+ *                               the diagonal, the diagonal included, in the order in which the solve adds
+ *                               them -- `dep` (position of the row it refers to, -1 for the diagonal) and
+ *                               `src` (where its value is found in `data`, `perm` applied).  HOST words
+ *                               info_host[0..3]: kept entries, reach (largest distance from the end of a
+ *                               row's level back to the position of one of its dependencies), longest row,
+ *                               widest level.  Synchronises `stream` once.
+ * nb200_sptrsv_solve_levels     the solve: a gather pass (values and right-hand sides into position order,
+ *                               as double), the cluster kernel, a scatter pass (x back into row order,
+ *                               rounded to the value type).  `workspace`:
+ *                               nb200_sptrsv_solve_levels_workspace_bytes(n, nrhs, entries).
+ *                               NB200_ERR_TOO_LARGE (nothing launched) when a ring of `reach` rows of
+ *                               nrhs doubles does not fit into the cluster's shared memory (200 KiB per
+ *                               CTA): the caller then uses nb200_sptrsv_solve.
+ * ------------------------------------------------------------------------------------------- */
+NB200_API int nb200_sptrsv_analyse_levels(int64_t n, int64_t nnz, const void* indices, const void* indptr,
+                                          int itype, int lower, int32_t* order, int32_t* level_ptr,
+                                          int64_t* nlevels_host, void* workspace, size_t workspace_bytes,
+                                          nb200_stream stream);
+NB200_API size_t nb200_sptrsv_level_plan_workspace_bytes(int64_t n);
+NB200_API int nb200_sptrsv_level_plan(int64_t n, int64_t nnz, const void* indices, const void* indptr, const void* perm,
+                                      int itype, int lower, const int32_t* order, const int32_t* level_ptr,
+                                      int64_t nlevels, int32_t* pos_ptr, int32_t* dep, int32_t* src, int64_t* info_host,
+                                      void* workspace, size_t workspace_bytes, nb200_stream stream);
+NB200_API size_t nb200_sptrsv_solve_levels_workspace_bytes(int64_t n, int64_t nrhs, int64_t entries);
+NB200_API int nb200_sptrsv_solve_levels(int64_t n, int64_t nrhs, int64_t entries, const void* data, const int32_t* src,
+                                        const int32_t* pos_ptr, const int32_t* dep, const int32_t* order,
+                                        const int32_t* level_ptr, int64_t nlevels, int64_t reach, int unit,
+                                        const void* b, void* x, void* workspace, size_t workspace_bytes,
+                                        int cluster_ctas, int dtype, nb200_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Allocation-free float32 triangular solve.  No counterpart in the reference.
  *
  * Same computation and same results as nb200_sptrsv_solve with dtype NB200_F32, for callers that

@@ -46,6 +46,13 @@ SIGNATURES = {
     "nb200_sptrsv_analyse": (_int, [_i64, _i64, _vp, _vp, _vp, _vp, _int, _int, _vp, _vp, _vp, _sz, _vp]),
     "nb200_sptrsv_solve": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp, _vp, _vp, _vp, _i64,
                                   _int, _int, _int, _vp]),
+    "nb200_sptrsv_analyse_levels": (_int, [_i64, _i64, _vp, _vp, _int, _int, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "nb200_sptrsv_level_plan_workspace_bytes": (_sz, [_i64]),
+    "nb200_sptrsv_level_plan": (_int, [_i64, _i64, _vp, _vp, _vp, _int, _int, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
+                                       _vp, _sz, _vp]),
+    "nb200_sptrsv_solve_levels_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "nb200_sptrsv_solve_levels": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _vp,
+                                         _vp, _sz, _int, _int, _vp]),
     "nb200_sptrsv_solve_f32_noalloc_capacity": (_i64, []),
     "nb200_sptrsv_solve_f32_noalloc": (_int, [_i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp, _vp, _vp, _i64,
                                               _int, _vp]),

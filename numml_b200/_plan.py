@@ -198,19 +198,57 @@ class PatternPlan:
         key = ("sptrsv", bool(lower), bool(transposed))
         if key not in self.extra:
             idx, ptr, itype = self.csr()
-            t_indptr, t_indices, _, _ = self.transpose()
             if transposed:
-                idx, ptr, t_indices, t_indptr = t_indices, t_indptr, idx, ptr
+                t_indptr, t_indices, _, _ = self.transpose()
+                idx, ptr = t_indices, t_indptr
             n = self.rows
             dev = self.indices.device
             with torch.cuda.device(dev):
                 order = torch.empty(n, dtype=torch.int32, device=dev)
+                level_ptr = torch.empty(n + 1, dtype=torch.int32, device=dev)
                 wbytes = _cabi.lib().nb200_sptrsv_analysis_workspace_bytes(n)
                 work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
                 nlevels = ctypes.c_int64(0)
-                _cabi.call("nb200_sptrsv_analyse", n, self.nnz, _ptr(idx), _ptr(ptr), _ptr(t_indptr), _ptr(t_indices),
-                           itype, int(bool(lower)), _ptr(order), ctypes.byref(nlevels), _ptr(work), wbytes, _stream())
+                _cabi.call("nb200_sptrsv_analyse_levels", n, self.nnz, _ptr(idx), _ptr(ptr), itype, int(bool(lower)),
+                           _ptr(order), _ptr(level_ptr), ctypes.byref(nlevels), _ptr(work), wbytes, _stream())
+                self.extra[key + ("level_ptr",)] = level_ptr[:int(nlevels.value) + 1].clone()
+                _published(dev)
             self.extra[key] = (order, int(nlevels.value))
+        return self.extra[key]
+
+    def sptrsv_level_plan(self, lower, transposed=False):
+        """Position-ordered structure for the cluster solve (``nb200_sptrsv_level_plan``), or None for
+        an empty matrix: a dict with ``level_ptr, pos_ptr, dep, src`` (device int32 arrays) and the
+        host numbers ``entries, reach, longest_row, widest_level, nlevels``."""
+        key = ("sptrsv_levels", bool(lower), bool(transposed))
+        if key not in self.extra:
+            order, nlevels = self.sptrsv_order(lower, transposed)
+            n = self.rows
+            if n == 0 or nlevels == 0 or self.nnz >= 2 ** 31 - 1:
+                self.extra[key] = None
+                return None
+            level_ptr = self.extra[("sptrsv", bool(lower), bool(transposed), "level_ptr")]
+            idx, ptr, itype = self.csr()
+            perm = None
+            if transposed:
+                t_indptr, t_indices, perm, _ = self.transpose()
+                idx, ptr = t_indices, t_indptr
+            dev = self.indices.device
+            with torch.cuda.device(dev):
+                pos_ptr = torch.empty(n + 1, dtype=torch.int32, device=dev)
+                dep = torch.empty(max(self.nnz, 1), dtype=torch.int32, device=dev)
+                src = torch.empty(max(self.nnz, 1), dtype=torch.int32, device=dev)
+                wbytes = _cabi.lib().nb200_sptrsv_level_plan_workspace_bytes(n)
+                work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+                info = (ctypes.c_int64 * 4)()
+                _cabi.call("nb200_sptrsv_level_plan", n, self.nnz, _ptr(idx), _ptr(ptr), _ptr(perm) if perm is not None else None,
+                           itype, int(bool(lower)), _ptr(order), _ptr(level_ptr), nlevels, _ptr(pos_ptr), _ptr(dep), _ptr(src),
+                           info, _ptr(work), wbytes, _stream())
+                entries = int(info[0])
+                self.extra[key] = {"level_ptr": level_ptr, "pos_ptr": pos_ptr, "dep": dep[:max(entries, 1)].clone(),
+                                   "src": src[:max(entries, 1)].clone(), "entries": entries, "reach": int(info[1]),
+                                   "longest_row": int(info[2]), "widest_level": int(info[3]), "nlevels": nlevels}
+                _published(dev)
         return self.extra[key]
 
 

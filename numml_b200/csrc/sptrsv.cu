@@ -76,6 +76,18 @@ sptrsv_levels_kernel(int64_t n, const I* __restrict__ indices, const I* __restri
     }
 }
 
+// level_ptr[l] = first position of level l in the sorted order; level_ptr[nlevels] = n.  Levels are
+// contiguous (a row of level l > 0 has a dependency of level l - 1), so every word is written.
+__global__ void sptrsv_level_ptr_kernel(int64_t n, const uint32_t* __restrict__ sorted_level, int32_t nlevels,
+                                        int32_t* __restrict__ level_ptr) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n; p += stride) {
+        const uint32_t l = sorted_level[p];
+        if (p == 0 || sorted_level[p - 1] != l) level_ptr[l] = (int32_t)p;
+        if (p == n - 1) level_ptr[nlevels] = (int32_t)n;
+    }
+}
+
 __global__ void sptrsv_iota_kernel(int64_t n, uint32_t* __restrict__ v) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) v[i] = (uint32_t)i;
@@ -229,7 +241,7 @@ static size_t analysis_workspace_bytes(int64_t n) {
 
 template <typename I>
 int sptrsv_analyse(int64_t n, const I* indices, const I* indptr, bool lower,
-                   int32_t* order, int64_t* nlevels_host, void* workspace, size_t bytes, cudaStream_t st) {
+                   int32_t* order, int32_t* level_ptr, int64_t* nlevels_host, void* workspace, size_t bytes, cudaStream_t st) {
     *nlevels_host = 0;
     if (n == 0) return NB200_OK;
     const size_t m = (size_t)n;
@@ -262,6 +274,8 @@ int sptrsv_analyse(int64_t n, const I* indices, const I* indptr, bool lower,
     if (rc != NB200_OK) return rc;
     if (cudaMemcpyAsync(order, in_a ? val_a : val_b, m * sizeof(int32_t), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
         return NB200_ERR_CUDA;
+    if (level_ptr)
+        sptrsv_level_ptr_kernel<<<flat_grid(n), 256, 0, st>>>(n, in_a ? key_a : key_b, (int32_t)nlevels, level_ptr);
     return launch_status();
 }
 
@@ -303,7 +317,19 @@ extern "C" int nb200_sptrsv_analyse(int64_t n, int64_t nnz, const void* indices,
     if (n > 0 && (!indptr || !order || !workspace || (nnz > 0 && !indices))) return NB200_ERR_BAD_ARG;
     return NB200_DISPATCH_I(itype,
         (sptrsv_analyse<I>(n, (const I*)indices, (const I*)indptr, lower != 0,
-                           order, nlevels_host, workspace, workspace_bytes, as_stream(stream))));
+                           order, nullptr, nlevels_host, workspace, workspace_bytes, as_stream(stream))));
+}
+
+extern "C" int nb200_sptrsv_analyse_levels(int64_t n, int64_t nnz, const void* indices, const void* indptr,
+                                           int itype, int lower, int32_t* order, int32_t* level_ptr,
+                                           int64_t* nlevels_host, void* workspace, size_t workspace_bytes,
+                                           nb200_stream stream) {
+    if (n < 0 || nnz < 0 || !nlevels_host) return NB200_ERR_BAD_ARG;
+    if (n >= 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
+    if (n > 0 && (!indptr || !order || !level_ptr || !workspace || (nnz > 0 && !indices))) return NB200_ERR_BAD_ARG;
+    return NB200_DISPATCH_I(itype,
+        (sptrsv_analyse<I>(n, (const I*)indices, (const I*)indptr, lower != 0,
+                           order, level_ptr, nlevels_host, workspace, workspace_bytes, as_stream(stream))));
 }
 
 extern "C" int nb200_sptrsv_solve(int64_t n, int64_t nnz, int64_t nrhs,

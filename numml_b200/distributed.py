@@ -240,89 +240,121 @@ def dist_conjugate_gradient(A, b_local, iterations, x_local=None):
     return x, torch.stack(hist)
 
 
-def _fetch_rows(A, B, B_data):
-    """CSR of the rows of B that A's halo columns refer to, fetched from their owners.
-    Returns (data, indices[global cols], indptr) with one row per halo slot of A, and for every peer
-    that was served the positions in this rank's B arrays of the entries sent to it."""
-    halo = A.halo
-    dev = B_data.device
-    lens_local = (B.indptr[1:] - B.indptr[:-1])
-    lens_ext = halo.extend(lens_local)                       # row lengths of [local | halo] rows
-    halo_lens = lens_ext[halo.n_local:]
-    indptr = torch.zeros(halo.n_halo + 1, dtype=torch.int64, device=dev)
-    indptr[1:] = torch.cumsum(halo_lens, 0)
-    total = int(indptr[-1])
-    data = torch.empty(total, dtype=B_data.dtype, device=dev)
-    indices = torch.empty(total, dtype=torch.int64, device=dev)
-    ops, keep, sent_pos = [], [], {}
-    for p in halo.peers_out:                                 # rows of mine that rank p needs
-        rows = halo.send[p]
-        starts, cnts = B.indptr[rows], lens_local[rows]
-        pos = torch.repeat_interleave(starts - torch.cumsum(cnts, 0) + cnts, cnts) + torch.arange(int(cnts.sum()), device=dev)
-        sent_pos[p] = pos
-        v, c = B_data[pos].contiguous(), B.global_indices[pos].contiguous()
-        keep += [v, c]
-        if v.numel() > 0:
-            ops.append(dist.P2POp(dist.isend, v, halo._peer(p), group=halo.group))
-            ops.append(dist.P2POp(dist.isend, c, halo._peer(p), group=halo.group))
-    for p in halo.peers_in:
-        a, b = int(indptr[halo.recv_offsets[p]]), int(indptr[halo.recv_offsets[p] + halo.recv_counts[p]])
-        if b > a:
-            ops.append(dist.P2POp(dist.irecv, data[a:b], halo._peer(p), group=halo.group))
-            ops.append(dist.P2POp(dist.irecv, indices[a:b], halo._peer(p), group=halo.group))
-    HaloPlan._run(ops)
-    return data, indices, indptr, sent_pos
+class _FetchedRows:
+    """Structure of the rows of B that A's halo columns refer to, fetched once per pair of patterns:
+    the column indices and row pointers of the fetched rows, the extended structure ``[B_local ; fetched
+    rows]``, for every peer served the positions in this rank's B arrays of the entries it reads, and
+    for every peer read from the range of fetched entries that it owns.  Values travel per call."""
+
+    def __init__(self, A, B):
+        halo = A.halo
+        dev = B.indptr.device
+        lens_local = (B.indptr[1:] - B.indptr[:-1])
+        lens_ext = halo.extend(lens_local)                       # row lengths of [local | halo] rows
+        indptr = torch.zeros(halo.n_halo + 1, dtype=torch.int64, device=dev)
+        indptr[1:] = torch.cumsum(lens_ext[halo.n_local:], 0)
+        bounds = indptr.cpu()
+        total = int(bounds[-1])
+        indices = torch.empty(total, dtype=torch.int64, device=dev)
+        ops, keep, self.sent_pos, self.ranges_in = [], [], {}, {}
+        for p in halo.peers_out:                                 # rows of mine that rank p needs
+            rows = halo.send[p]
+            starts, cnts = B.indptr[rows], lens_local[rows]
+            pos = torch.repeat_interleave(starts - torch.cumsum(cnts, 0) + cnts, cnts) + torch.arange(int(cnts.sum()), device=dev)
+            self.sent_pos[p] = pos
+            c = B.global_indices[pos].contiguous()
+            keep.append(c)
+            if c.numel() > 0:
+                ops.append(dist.P2POp(dist.isend, c, halo._peer(p), group=halo.group))
+        for p in halo.peers_in:
+            a, b = int(bounds[halo.recv_offsets[p]]), int(bounds[halo.recv_offsets[p] + halo.recv_counts[p]])
+            self.ranges_in[p] = (a, b)
+            if b > a:
+                ops.append(dist.P2POp(dist.irecv, indices[a:b], halo._peer(p), group=halo.group))
+        HaloPlan._run(ops)
+        self.halo = halo
+        self.total = total
+        self.h_indptr = indptr
+        self.nb = int(B.indptr[-1])
+        self.ext_indices = torch.cat((B.global_indices, indices))
+        self.ext_indptr = torch.cat((B.indptr, indptr[1:] + B.indptr[-1]))
+
+    def values(self, B_data):
+        """``[B_local values ; values of the fetched rows]`` for the current values of B."""
+        halo = self.halo
+        ext = torch.empty(self.nb + self.total, dtype=B_data.dtype, device=B_data.device)
+        ext[:self.nb] = B_data
+        ops, keep = [], []
+        for p in halo.peers_out:
+            v = B_data[self.sent_pos[p]]
+            keep.append(v)
+            if v.numel() > 0:
+                ops.append(dist.P2POp(dist.isend, v, halo._peer(p), group=halo.group))
+        for p in halo.peers_in:
+            a, b = self.ranges_in[p]
+            if b > a:
+                ops.append(dist.P2POp(dist.irecv, ext[self.nb + a:self.nb + b], halo._peer(p), group=halo.group))
+        HaloPlan._run(ops)
+        return ext
+
+
+def _fetched_rows(A, B):
+    """The cached ``_FetchedRows`` of the pair (collective on the first call for a pair of patterns:
+    every rank of the group reaches it in the same call, as the patterns change on all ranks alike)."""
+    key = (id(A.halo), B.indptr.data_ptr(), B.indptr._version, B.global_indices.data_ptr(), B.global_indices._version)
+    cache = B.__dict__.setdefault("_fetched_rows", {})
+    hit = cache.get(key)
+    if hit is None:
+        cache.clear()
+        hit = cache[key] = _FetchedRows(A, B)
+    return hit
 
 
 class _DistSpGEMM(torch.autograd.Function):
     """C = A B on row blocks.  Forward: the rows of B that this rank's columns refer to are fetched
-    from their owners and the local product is formed against ``[B_local ; fetched rows]``.
-    Backward: the local SpGEMM backward gives grad_A (local) and a gradient for every entry of the
-    extended B; the part that belongs to fetched rows travels back to the owners, who add it to
-    their own in ascending peer order (reproducible)."""
+    from their owners (structure once per pair of patterns, values per call) and the local product is
+    formed against ``[B_local ; fetched rows]``.  Backward: the local SpGEMM backward gives grad_A
+    (local) and a gradient for every entry of the extended B; the part that belongs to fetched rows
+    travels back to the owners, who add it to their own in ascending peer order (reproducible)."""
 
     @staticmethod
     def forward(ctx, A, B, A_data, B_data):
         halo = A.halo
-        B_values = B_data.detach()
-        h_data, h_indices, h_indptr, sent_pos = _fetch_rows(A, B, B_values)
+        fetched = _fetched_rows(A, B)
+        ext_data = fetched.values(B_data.detach())
         n_ext = halo.n_local + halo.n_halo
-        ext_data = torch.cat((B_values, h_data))
-        ext_indices = torch.cat((B.global_indices, h_indices))
-        ext_indptr = torch.cat((B.indptr, h_indptr[1:] + B.indptr[-1]))
         C_data, C_indices, C_indptr = A.ops.spgemm_forward(A.n_rows, n_ext, A_data.detach(), A.indices, A.indptr,
-                                                           n_ext, B.global_shape[1], ext_data, ext_indices, ext_indptr)
-        ctx.A, ctx.B = A, B
-        ctx.sent_pos, ctx.h_indptr = sent_pos, h_indptr
-        ctx.save_for_backward(A_data, ext_data, ext_indices, ext_indptr, C_indices, C_indptr)
+                                                           n_ext, B.global_shape[1], ext_data, fetched.ext_indices,
+                                                           fetched.ext_indptr)
+        ctx.A, ctx.B, ctx.fetched = A, B, fetched
+        ctx.save_for_backward(A_data, ext_data, C_indices, C_indptr)
         ctx.mark_non_differentiable(C_indices, C_indptr)
         return C_data, C_indices, C_indptr
 
     @staticmethod
     def backward(ctx, grad_C, _grad_indices, _grad_indptr):
-        A, B = ctx.A, ctx.B
+        A, B, fetched = ctx.A, ctx.B, ctx.fetched
         halo = A.halo
-        A_data, ext_data, ext_indices, ext_indptr, C_indices, C_indptr = ctx.saved_tensors
+        A_data, ext_data, C_indices, C_indptr = ctx.saved_tensors
         n_ext = halo.n_local + halo.n_halo
         grad_A, grad_ext = A.ops.spgemm_backward(grad_C.contiguous(), C_indices, C_indptr,
                                                  A.n_rows, n_ext, A_data.detach(), A.indices, A.indptr,
-                                                 n_ext, B.global_shape[1], ext_data, ext_indices, ext_indptr)
-        nb = int(B.indptr[-1])
+                                                 n_ext, B.global_shape[1], ext_data, fetched.ext_indices, fetched.ext_indptr)
+        nb = fetched.nb
         grad_B = grad_ext[:nb].clone()
         ops, bufs = [], {}
         for p in halo.peers_in:                              # gradients of the rows fetched from p go home
-            a = int(ctx.h_indptr[halo.recv_offsets[p]])
-            b = int(ctx.h_indptr[halo.recv_offsets[p] + halo.recv_counts[p]])
+            a, b = fetched.ranges_in[p]
             if b > a:
-                ops.append(dist.P2POp(dist.isend, grad_ext[nb + a:nb + b].contiguous(), halo._peer(p), group=halo.group))
+                ops.append(dist.P2POp(dist.isend, grad_ext[nb + a:nb + b], halo._peer(p), group=halo.group))
         for p in halo.peers_out:
-            count = int(ctx.sent_pos[p].numel())
+            count = int(fetched.sent_pos[p].numel())
             if count > 0:
                 bufs[p] = torch.empty(count, dtype=grad_ext.dtype, device=grad_ext.device)
                 ops.append(dist.P2POp(dist.irecv, bufs[p], halo._peer(p), group=halo.group))
         HaloPlan._run(ops)
         for p in sorted(bufs):
-            grad_B.index_add_(0, ctx.sent_pos[p], bufs[p])
+            grad_B.index_add_(0, fetched.sent_pos[p], bufs[p])
         return None, None, grad_A, grad_B
 
 

@@ -402,6 +402,12 @@ def spgemm_backward(grad_C, C_indices, C_indptr, A_rows, A_cols, A_data, A_indic
 sptrsv_wait_budget_cycles = 2_000_000_000
 _RESIDENT_THREADS = 148 * 2048               # threads a B200 keeps resident at once
 sptrsv_check_status = True
+# Which solve kernel runs: "auto" takes the cluster kernel (levels one after the other inside one
+# thread-block cluster, unknowns exchanged through distributed shared memory) for patterns with narrow
+# dependency levels and the grid-wide sync-free kernel otherwise; "syncfree" / "cluster" force one of
+# them ("cluster" still falls back when the ring of recent rows cannot fit).  Results are identical.
+sptrsv_kernel = "auto"
+sptrsv_cluster_ctas = 8
 
 
 def check_status(device=None):
@@ -427,11 +433,41 @@ def _team_lanes(n, nlevels):
     return lanes
 
 
-def _solve(plan, data, idx, ptr, perm, itype, order, nlevels, lower, unit, b):
+def _cluster_solve_fits(levels, n, nrhs, forced=False):
+    """Whether the cluster solve is taken for this pattern and number of right-hand sides: its ring must
+    hold `reach` rows of nrhs doubles within 200 KiB per CTA, the mean level must fit into two rounds of the
+    cluster's teams (wider levels keep the whole GPU busy with the sync-free kernel), and rows must be short
+    (the first eight entries of a row are prefetched, the rest is read on the critical path)."""
+    if levels is None or nrhs < 1:
+        return False
+    ctas = sptrsv_cluster_ctas
+    cap = 1
+    while ctas * cap < levels["reach"]:
+        cap *= 2
+    lanes = 1
+    while lanes < 32 and lanes < nrhs:
+        lanes *= 2
+    teams = ctas * 512 // lanes
+    if cap * nrhs * 8 > 200 * 1024:
+        return False
+    return forced or (n <= 2 * teams * levels["nlevels"] and levels["longest_row"] <= 32)
+
+
+def _solve(plan, data, idx, ptr, perm, itype, order, nlevels, lower, unit, b, transposed=False):
     n = plan.rows
     nrhs = 1 if b.ndim == 1 else int(b.shape[1])
     dev = b.device
     x = torch.empty_like(b)
+    if sptrsv_kernel in ("auto", "cluster") and n > 0 and nrhs > 0:
+        levels = plan.sptrsv_level_plan(lower, transposed)
+        if _cluster_solve_fits(levels, n, nrhs, forced=sptrsv_kernel == "cluster"):
+            wbytes = _cabi.lib().nb200_sptrsv_solve_levels_workspace_bytes(n, nrhs, levels["entries"])
+            work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+            _cabi.call("nb200_sptrsv_solve_levels", n, nrhs, levels["entries"], _ptr(data), _ptr(levels["src"]),
+                       _ptr(levels["pos_ptr"]), _ptr(levels["dep"]), _ptr(order), _ptr(levels["level_ptr"]), nlevels,
+                       levels["reach"], int(bool(unit)), _ptr(b), _ptr(x), _ptr(work), wbytes, int(sptrsv_cluster_ctas),
+                       _dtype_code(data), _stream())
+            return x
     xd = torch.empty(n * nrhs, dtype=torch.float64, device=dev) if b.dtype == torch.float32 else None
     status = _status_word(dev)
     _cabi.call("nb200_sptrsv_solve", n, plan.nnz, nrhs, _ptr(data), _ptr(idx), _ptr(ptr),
@@ -476,7 +512,8 @@ def sptrsv_backward(grad_x, x, A_rows, A_cols, A_data, A_indices, A_indptr, lowe
         t_indptr, t_indices, t_perm, _ = plan.transpose()
         order_t, nlevels_t = plan.sptrsv_order(not lower, transposed=True)
         # grad_b = A^{-T} grad_x: the opposite-triangle solve on the transposed structure
-        grad_b = _solve(plan, A_data, t_indices, t_indptr, t_perm, itype, order_t, nlevels_t, not lower, unit, grad_x)
+        grad_b = _solve(plan, A_data, t_indices, t_indptr, t_perm, itype, order_t, nlevels_t, not lower, unit, grad_x,
+                        transposed=True)
         grad_A = torch.empty_like(A_data)
         _cabi.call("nb200_masked_outer", A_rows, plan.nnz, nrhs, _ptr(idx), _ptr(ptr), _ptr(grad_b), _ptr(x), -1.0,
                    _ptr(grad_A), _dtype_code(A_data), itype, _stream())

@@ -76,6 +76,14 @@ def _worker(rank, world, init_file, case):
         Cd2.backward(gC[a:b])
         assert torch.allclose(A.data.grad, gA3_ref[sl], rtol=1e-13, atol=1e-13)
         assert torch.allclose(Bm.data.grad, gB3_ref[sl], rtol=1e-12, atol=1e-13)
+        # second product on the cached structure of the fetched rows, with other values in B
+        with torch.no_grad():
+            Bm.data.mul_(-0.5)
+        Cd3, Ci3, Cp3 = A @ Bm
+        C3_ref = oracle.spgemm_forward(m, n, d, i, p, m, n, -0.5 * d, i, p)
+        assert torch.equal(Cp3, Cp) and torch.equal(Ci3, Ci)
+        assert torch.allclose(Cd3.detach(), C3_ref[0][a:b], rtol=1e-13, atol=1e-13)
+        assert len(Bm._fetched_rows) == 1
 
         # ---- CG with all-reduced dots (SPD case only) -----------------------------------------
         if case == "stencil":

@@ -12,10 +12,15 @@ from numml_b200 import workloads as W
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def ops():
+@pytest.fixture(params=["syncfree", "cluster", "auto"])
+def ops(request):
+    """The operator shim with the solve kernel forced to the grid-wide sync-free one, to the cluster
+    kernel (taken whenever its ring of recent rows fits), or left to choose."""
     from numml_b200 import numml_torch_cpp
-    return numml_torch_cpp
+    before = numml_torch_cpp.sptrsv_kernel
+    numml_torch_cpp.sptrsv_kernel = request.param
+    yield numml_torch_cpp
+    numml_torch_cpp.sptrsv_kernel = before
 
 
 def test_golden_sptrsv(golden_ops, ops):
@@ -150,3 +155,32 @@ def test_shape_checks(ops):
         ops.sptrsv_forward(10, 11, d.cuda(), i.cuda(), p.cuda(), True, False, torch.ones(10, dtype=torch.float64, device="cuda"))
     with pytest.raises(RuntimeError, match="right-hand side"):
         ops.sptrsv_forward(10, 10, d.cuda(), i.cuda(), p.cuda(), True, False, torch.ones(9, dtype=torch.float64, device="cuda"))
+
+
+@pytest.mark.parametrize("nrhs,ctas", [(16, 8), (1, 8), (3, 4), (16, 16), (40, 8)])
+def test_cluster_kernel_matches_syncfree_at_scale(nrhs, ctas):
+    """512^2 grid (1534 narrow levels): the cluster kernel and the grid-wide kernel give the same bits,
+    forward and backward, for cluster sizes 4 / 8 / 16 and right-hand-side counts below, at and above
+    the lanes of a team."""
+    from numml_b200 import numml_torch_cpp as ops
+    n = 512
+    d, i, p, (m, _) = W.poisson2d_9pt_lower(n, torch.float64)
+    dd, di, dp = d.cuda(), i.cuda(), p.cuda()
+    gen = torch.Generator("cuda").manual_seed(nrhs)
+    shape = (m,) if nrhs == 1 else (m, nrhs)
+    B = torch.randn(shape, dtype=torch.float64, device="cuda", generator=gen)
+    GX = torch.randn(shape, dtype=torch.float64, device="cuda", generator=gen)
+    before = ops.sptrsv_kernel, ops.sptrsv_cluster_ctas
+    try:
+        ops.sptrsv_kernel = "syncfree"
+        X0 = ops.sptrsv_forward(m, m, dd, di, dp, True, False, B)
+        gA0, gB0 = ops.sptrsv_backward(GX, X0, m, m, dd, di, dp, True, False, B)
+        ops.sptrsv_kernel, ops.sptrsv_cluster_ctas = "cluster", ctas
+        X1 = ops.sptrsv_forward(m, m, dd, di, dp, True, False, B)
+        gA1, gB1 = ops.sptrsv_backward(GX, X1, m, m, dd, di, dp, True, False, B)
+    finally:
+        ops.sptrsv_kernel, ops.sptrsv_cluster_ctas = before
+    assert torch.equal(X0, X1) and torch.equal(gB0, gB1) and torch.equal(gA0, gA1)
+    from numml_b200 import _plan
+    levels = _plan.get_plan(m, m, di, dp).sptrsv_level_plan(True)
+    assert levels["nlevels"] == 3 * n - 2 and levels["longest_row"] == 5 and levels["reach"] <= 5 * n
