@@ -230,6 +230,18 @@ def config5(rep, ops, W, cpu, n=1024):
             "one right-hand side x 16", f"{levels} dependency levels: latency-bound; first call with the one-off analysis {first_ms:.1f} ms")
     rep.add(name, "SpTRSV backward", gpu_ms(lambda: ops.sptrsv_backward(G, X, m, m, dd, di, dp, True, False, B), 5, 1), bb, c_b,
             "one right-hand side x 16 (the reference transposes per call)", "")
+    # the optional cluster kernel (levels inside one thread-block cluster, unknowns through distributed shared memory)
+    before = ops.sptrsv_kernel, ops.sptrsv_cluster_ctas
+    try:
+        for ctas in (8, 16):
+            ops.sptrsv_kernel, ops.sptrsv_cluster_ctas = "cluster", ctas
+            Xc = ops.sptrsv_forward(m, m, dd, di, dp, True, False, B)
+            same = "same bits as the sync-free kernel" if torch.equal(Xc, X) else "DIFFERS from the sync-free kernel"
+            rep.add(name, f"SpTRSV forward, cluster kernel ({ctas} CTAs)",
+                    gpu_ms(lambda: ops.sptrsv_forward(m, m, dd, di, dp, True, False, B), 5, 1), fb, None, "",
+                    f"opt-in (sptrsv_kernel = 'cluster'); {same}")
+    finally:
+        ops.sptrsv_kernel, ops.sptrsv_cluster_ctas = before
 
 
 def config6(rep, W, n=1 << 22):

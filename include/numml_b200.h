@@ -549,6 +549,16 @@ NB200_API int nb200_splu_numeric(int64_t n, void* Mt_data, const int64_t* Mt_ind
  * a rank reaches the publish of step t only after its pull of step t-1 has seen every neighbour's flag
  * at t-1, and a neighbour raises that flag only after its own pull of step t-2 has finished.
  *
+ * Rows of a dense operand (row-partitioned SpMM) travel the same way, an item being a row of `row_bytes`
+ * bytes (a multiple of 16; `dst` / `grad` 16-byte aligned).  A rank publishes its whole block of rows once
+ * with nb200_halo_publish (idx = NULL); every neighbour gathers the rows it needs from there:
+ * nb200_halo_pull_rows       descriptor words: [0] address of the neighbour's area, [1] rows per half,
+ *                            [2] first halo slot of this neighbour in `row_of_slot`, [3] number of slots,
+ *                            [4] first destination row in `dst`, [5] address of its flag word; slot h of the
+ *                            segment receives row row_of_slot[[2] + h] of the neighbour's block.
+ * nb200_halo_pull_add_rows   nb200_halo_pull_add on rows: grad row target[j] += rows source_elem[c] of the
+ *                            packed areas of neighbours source_peer[c], in that order (unfused adds).
+ *
  * nb200_ipc_alloc / nb200_ipc_open / nb200_ipc_close / nb200_ipc_free create an exchange buffer (zeroed,
  * from cudaMalloc, since memory that other processes map cannot come out of a caching allocator's
  * segment; this is the only allocation the library ever makes, at set-up time), export it as 64 opaque
@@ -564,6 +574,13 @@ NB200_API int nb200_halo_pull_add(int npeers, const int64_t* desc, int64_t ntarg
                                   const int64_t* target_ptr, const int32_t* source_peer, const int64_t* source_elem,
                                   void* grad, const int32_t* step_word, int32_t* status, int64_t wait_budget_cycles,
                                   int dtype, nb200_stream stream);
+NB200_API int nb200_halo_pull_rows(int npeers, const int64_t* desc, const int64_t* row_of_slot, int64_t largest_segment,
+                                   int64_t row_bytes, void* dst, const int32_t* step_word, int32_t* status,
+                                   int64_t wait_budget_cycles, nb200_stream stream);
+NB200_API int nb200_halo_pull_add_rows(int npeers, const int64_t* desc, int64_t ntargets, const int64_t* target,
+                                       const int64_t* target_ptr, const int32_t* source_peer, const int64_t* source_elem,
+                                       int64_t row_bytes, void* grad, const int32_t* step_word, int32_t* status,
+                                       int64_t wait_budget_cycles, int dtype, nb200_stream stream);
 NB200_API int nb200_ipc_alloc(size_t bytes, void** ptr, void* handle64);
 NB200_API int nb200_ipc_open(const void* handle64, void** ptr);
 NB200_API int nb200_ipc_close(void* ptr);

@@ -77,6 +77,8 @@ SIGNATURES = {
     "nb200_halo_publish": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _int, _vp, _int, _vp]),
     "nb200_halo_pull": (_int, [_int, _vp, _i64, _vp, _vp, _vp, _i64, _int, _vp]),
     "nb200_halo_pull_add": (_int, [_int, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp]),
+    "nb200_halo_pull_rows": (_int, [_int, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "nb200_halo_pull_add_rows": (_int, [_int, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _int, _vp]),
     "nb200_ipc_alloc": (_int, [_sz, _c.POINTER(_vp), _vp]),
     "nb200_ipc_open": (_int, [_vp, _c.POINTER(_vp)]),
     "nb200_ipc_close": (_int, [_vp]),

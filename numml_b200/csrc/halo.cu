@@ -127,6 +127,104 @@ halo_pull_add_kernel(int npeers, const int64_t* __restrict__ desc, int64_t ntarg
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Rows of a dense operand (SpMM): the same protocol, items are rows of `w16` 16-byte units.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld_fresh(const uint4* p) { return __ldcv(p); }
+
+// Row descriptor (int64 words, kHaloDescWords per neighbour):
+//   [0] address of the neighbour's area (2 halves of [1] rows each)   [1] rows per half
+//   [2] first halo slot of this neighbour in `row_of_slot`            [3] number of slots
+//   [4] first destination row in this rank's matrix                   [5] address of the neighbour's flag word
+// Slot h of the segment receives row row_of_slot[[2] + h] of the neighbour's published block.
+__global__ void __launch_bounds__(kHaloThreads)
+halo_pull_rows_kernel(const int64_t* __restrict__ desc, const int64_t* __restrict__ row_of_slot, int64_t w16,
+                      uint4* dst_base, const int* step_word, int32_t* status, long long budget) {
+    const int64_t* d = desc + (int64_t)blockIdx.y * kHaloDescWords;
+    const int t = *step_word;
+    __shared__ int ready;
+    if (threadIdx.x == 0) {
+        ready = wait_for_step(reinterpret_cast<const int*>(d[5]), t, budget) ? 1 : 0;
+        if (!ready && status) atomicExch(status, (int)NB200_ERR_WAIT_BUDGET);
+    }
+    __syncthreads();
+    if (!ready) return;
+    const uint4* half = reinterpret_cast<const uint4*>(d[0]) + (size_t)(t & 1) * (size_t)d[1] * (size_t)w16;
+    const int64_t* rows = row_of_slot + d[2];
+    uint4* dst = dst_base + (size_t)d[4] * (size_t)w16;
+    const int64_t units = d[3] * w16, stride = (int64_t)gridDim.x * blockDim.x;
+    constexpr int U = 4;                                        // remote loads in flight per thread
+    for (int64_t k0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k0 < units; k0 += U * stride) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t k = k0 + u * stride;
+            if (k < units) {
+                const int64_t h = k / w16, c = k - h * w16;
+                v[u] = ld_fresh(half + rows[h] * w16 + c);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t k = k0 + u * stride;
+            if (k < units) dst[k] = v[u];
+        }
+    }
+}
+
+template <typename T> struct Unit16;
+template <> struct Unit16<float> {
+    static __device__ __forceinline__ uint4 add(uint4 a, uint4 b) {
+        a.x = __float_as_uint(__fadd_rn(__uint_as_float(a.x), __uint_as_float(b.x)));
+        a.y = __float_as_uint(__fadd_rn(__uint_as_float(a.y), __uint_as_float(b.y)));
+        a.z = __float_as_uint(__fadd_rn(__uint_as_float(a.z), __uint_as_float(b.z)));
+        a.w = __float_as_uint(__fadd_rn(__uint_as_float(a.w), __uint_as_float(b.w)));
+        return a;
+    }
+};
+template <> struct Unit16<double> {
+    static __device__ __forceinline__ uint4 add(uint4 a, uint4 b) {
+        const double lo = __dadd_rn(__hiloint2double((int)a.y, (int)a.x), __hiloint2double((int)b.y, (int)b.x));
+        const double hi = __dadd_rn(__hiloint2double((int)a.w, (int)a.z), __hiloint2double((int)b.w, (int)b.z));
+        a.x = (unsigned)__double2loint(lo); a.y = (unsigned)__double2hiint(lo);
+        a.z = (unsigned)__double2loint(hi); a.w = (unsigned)__double2hiint(hi);
+        return a;
+    }
+};
+
+// grad row target[j] += the rows source_elem[c] of the neighbours source_peer[c], c in target_ptr[j] ..
+// target_ptr[j + 1], neighbours in ascending order; descriptor words [0], [1] (rows per half), [5] are used.
+template <typename T>
+__global__ void __launch_bounds__(kHaloThreads)
+halo_pull_add_rows_kernel(int npeers, const int64_t* __restrict__ desc, int64_t ntargets,
+                          const int64_t* __restrict__ target, const int64_t* __restrict__ target_ptr,
+                          const int32_t* __restrict__ source_peer, const int64_t* __restrict__ source_elem,
+                          int64_t w16, uint4* grad, const int* step_word, int32_t* status, long long budget) {
+    const int t = *step_word;
+    __shared__ int ready;
+    if (threadIdx.x == 0) {
+        int ok = 1;
+        for (int p = 0; p < npeers && ok; ++p)
+            ok = wait_for_step(reinterpret_cast<const int*>(desc[(int64_t)p * kHaloDescWords + 5]), t, budget) ? 1 : 0;
+        if (!ok && status) atomicExch(status, (int)NB200_ERR_WAIT_BUDGET);
+        ready = ok;
+    }
+    __syncthreads();
+    if (!ready) return;
+    const int64_t units = ntargets * w16, stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < units; k += stride) {
+        const int64_t j = k / w16, c = k - j * w16;
+        uint4* home = grad + target[j] * w16 + c;
+        uint4 acc = *home;
+        for (int64_t q = target_ptr[j]; q < target_ptr[j + 1]; ++q) {
+            const int64_t* d = desc + (int64_t)source_peer[q] * kHaloDescWords;
+            const uint4* half = reinterpret_cast<const uint4*>(d[0]) + (size_t)(t & 1) * (size_t)d[1] * (size_t)w16;
+            acc = Unit16<T>::add(acc, ld_fresh(half + source_elem[q] * w16 + c));
+        }
+        *home = acc;
+    }
+}
+
 static inline unsigned halo_grid(int64_t count, int cap) {
     const int64_t want = ceil_div(count > 0 ? count : 1, (int64_t)kHaloThreads);
     return (unsigned)(want < cap ? want : cap);
@@ -140,7 +238,7 @@ extern "C" int nb200_halo_publish(int64_t count, const void* src, const int64_t*
                                   int32_t* step_word, int bump_step, uint32_t* arrivals, int dtype, nb200_stream stream) {
     if (count < 0 || !area || !flag || !step_word || !arrivals || (count > 0 && !src)) return NB200_ERR_BAD_ARG;
     cudaStream_t st = as_stream(stream);
-    const unsigned grid = halo_grid(count, 64);
+    const unsigned grid = halo_grid(count, count > (int64_t)1 << 22 ? kSMs * 8 : 64);
     return NB200_DISPATCH_T(dtype,
         (halo_publish_kernel<T><<<grid, kHaloThreads, 0, st>>>(count, (const T*)src, idx, (T*)area, flag, step_word,
                                                                bump_step, arrivals), launch_status()));
@@ -170,6 +268,40 @@ extern "C" int nb200_halo_pull_add(int npeers, const int64_t* desc, int64_t ntar
     return NB200_DISPATCH_T(dtype,
         (halo_pull_add_kernel<T><<<halo_grid(ntargets, 128), kHaloThreads, 0, st>>>(
              npeers, desc, ntargets, target, target_ptr, source_peer, source_elem, (T*)grad, step_word, status, budget),
+         launch_status()));
+}
+
+extern "C" int nb200_halo_pull_rows(int npeers, const int64_t* desc, const int64_t* row_of_slot, int64_t largest_segment,
+                                    int64_t row_bytes, void* dst, const int32_t* step_word, int32_t* status,
+                                    int64_t wait_budget_cycles, nb200_stream stream) {
+    if (npeers < 0 || largest_segment < 0 || row_bytes <= 0 || (row_bytes & 15) != 0 || !step_word) return NB200_ERR_BAD_ARG;
+    if (npeers == 0) return NB200_OK;
+    if (!desc || !row_of_slot || !dst) return NB200_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(dst) & 15) != 0) return NB200_ERR_ALIGN;
+    const int64_t w16 = row_bytes / 16;
+    int per_peer = (kSMs * 8) / npeers;
+    if (per_peer < 8) per_peer = 8;
+    const dim3 grid(halo_grid(largest_segment * w16, per_peer), (unsigned)npeers);
+    const long long budget = wait_budget_cycles > 0 ? wait_budget_cycles : 4000000000LL;
+    halo_pull_rows_kernel<<<grid, kHaloThreads, 0, as_stream(stream)>>>(desc, row_of_slot, w16, (uint4*)dst, step_word,
+                                                                       status, budget);
+    return launch_status();
+}
+
+extern "C" int nb200_halo_pull_add_rows(int npeers, const int64_t* desc, int64_t ntargets, const int64_t* target,
+                                        const int64_t* target_ptr, const int32_t* source_peer, const int64_t* source_elem,
+                                        int64_t row_bytes, void* grad, const int32_t* step_word, int32_t* status,
+                                        int64_t wait_budget_cycles, int dtype, nb200_stream stream) {
+    if (npeers < 0 || ntargets < 0 || row_bytes <= 0 || (row_bytes & 15) != 0 || !step_word) return NB200_ERR_BAD_ARG;
+    if (npeers == 0 || ntargets == 0) return NB200_OK;
+    if (!desc || !target || !target_ptr || !source_peer || !source_elem || !grad) return NB200_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(grad) & 15) != 0) return NB200_ERR_ALIGN;
+    const int64_t w16 = row_bytes / 16;
+    const long long budget = wait_budget_cycles > 0 ? wait_budget_cycles : 4000000000LL;
+    cudaStream_t st = as_stream(stream);
+    return NB200_DISPATCH_T(dtype,
+        (halo_pull_add_rows_kernel<T><<<halo_grid(ntargets * w16, kSMs * 8), kHaloThreads, 0, st>>>(
+             npeers, desc, ntargets, target, target_ptr, source_peer, source_elem, w16, (uint4*)grad, step_word, status, budget),
          launch_status()));
 }
 

@@ -146,8 +146,9 @@ class HaloPlan:
 class _DistMatVec(torch.autograd.Function):
     @staticmethod
     def forward(ctx, A, data, x_local):
-        x_ext = A.halo.extend(x_local.detach())
-        ctx.A = A
+        rows = _row_exchange(A, x_local)
+        x_ext = rows.extend(x_local.detach()) if rows is not None else A.halo.extend(x_local.detach())
+        ctx.A, ctx.rows = A, rows
         ctx.save_for_backward(data, x_ext)
         n_ext = A.halo.n_local + A.halo.n_halo
         if x_local.ndim == 1:
@@ -164,6 +165,8 @@ class _DistMatVec(torch.autograd.Function):
             grad_A, grad_x_ext = A.ops.spgemv_backward(g, A.n_rows, n_ext, data, A.indices, A.indptr, x_ext)
         else:
             grad_A, grad_x_ext = A.ops.spdmm_backward(A.n_rows, n_ext, data, A.indices, A.indptr, x_ext, g)
+        if ctx.rows is not None:
+            return None, grad_A, ctx.rows.reduce(grad_x_ext)
         return None, grad_A, A.halo.reduce(grad_x_ext)
 
 
@@ -589,6 +592,191 @@ class PeerExchange:
             self.base = None
 
 
+class PeerRowExchange:
+    """Exchange of the rows of a dense operand between row blocks through peer memory, for the
+    row-partitioned SpMM (``csrc/halo.cu``, the row kernels).  One buffer per rank from
+    ``nb200_ipc_alloc``, mapped by every neighbour: ``[flag words: 256 bytes][this rank's block of rows,
+    2 halves][partial gradient rows per halo slot, 2 halves]``.
+
+    forward   every rank copies its block of X into its buffer once (``nb200_halo_publish``), each
+              neighbour gathers the rows it needs from there straight into ``[local | halo]``
+              (``nb200_halo_pull_rows``): nothing is packed per neighbour and no communication library runs;
+    backward  the halo part of the extended gradient is published, and every owner adds the rows that
+              belong to it, neighbours in ascending order (``nb200_halo_pull_add_rows``), which is the
+              order of the send/recv path: the results are the same bit for bit.
+
+    Collective over the halo plan's group.  ``usable`` is False on every rank alike when the neighbour
+    relation is not symmetric, a row is not a multiple of 16 bytes, or a mapping failed."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, halo, dtype, width, device):
+        import ctypes
+        from . import _cabi
+        self._c, self._cabi = ctypes, _cabi
+        self.halo, self.device, self.width = halo, device, int(width)
+        self.esize = torch.empty(0, dtype=dtype).element_size()
+        self.code = _cabi.F64 if dtype == torch.float64 else _cabi.F32
+        self.row_bytes = self.width * self.esize
+        self.base, self.mapped = None, {}
+        self.wait_budget_cycles = 4_000_000_000
+        group = halo.group
+        peers = sorted(set(halo.peers_in) | set(halo.peers_out))
+        ok = set(halo.peers_in) == set(halo.peers_out) and len(peers) > 0 and self.row_bytes % 16 == 0 \
+            and dtype in (torch.float32, torch.float64)
+        pad = lambda b: (b + 255) // 256 * 256  # noqa: E731
+        self.x_off = self.FLAG_BYTES
+        self.g_off = self.x_off + pad(2 * halo.n_local * self.row_bytes)
+        total = self.g_off + pad(2 * max(halo.n_halo, 1) * self.row_bytes)
+        handle = (ctypes.c_ubyte * 64)()
+        if ok:
+            with torch.cuda.device(device):
+                ptr = ctypes.c_void_p()
+                ok = _cabi.lib().nb200_ipc_alloc(total, ctypes.byref(ptr), handle) == 0
+                if ok:
+                    self.base = ptr.value
+        meta = {"ok": ok, "handle": bytes(handle), "x_off": self.x_off, "g_off": self.g_off, "n_local": halo.n_local,
+                "n_halo": halo.n_halo, "recv_offsets": list(halo.recv_offsets)}
+        metas = [None] * halo.world
+        dist.all_gather_object(metas, meta, group=group)
+        ok = all(m["ok"] for m in metas)
+        if ok:
+            with torch.cuda.device(device):
+                for p in peers:
+                    ptr = ctypes.c_void_p()
+                    buf = (ctypes.c_ubyte * 64).from_buffer_copy(metas[p]["handle"])
+                    if _cabi.lib().nb200_ipc_open(buf, ctypes.byref(ptr)) != 0:
+                        ok = False
+                        break
+                    self.mapped[p] = ptr.value
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        self.usable = bool(flag.item())
+        if not self.usable:
+            self.close()
+            return
+        dev = device
+        self.step_word = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.arrivals = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        # forward: which row of the owner's block goes into which halo slot
+        self.row_of_slot = torch.cat([halo.need[p] - halo.col_bounds[p] for p in halo.peers_in]).contiguous()
+        words = []
+        for p in halo.peers_in:
+            m = metas[p]
+            words += [self.mapped[p] + m["x_off"], m["n_local"], halo.recv_offsets[p], halo.recv_counts[p],
+                      halo.n_local + halo.recv_offsets[p], self.mapped[p] + 0, 0, 0]
+        self.x_desc = torch.tensor(words, dtype=torch.int64, device=dev)
+        self.x_largest = max([halo.recv_counts[p] for p in halo.peers_in], default=0)
+        # backward: for every local row that a neighbour reads, the halo slots (of the neighbours) that hold
+        # partial gradient rows for it, neighbours ascending
+        words, index_of = [], {}
+        for q, p in enumerate(halo.peers_out):
+            m = metas[p]
+            index_of[p] = q
+            words += [self.mapped[p] + m["g_off"], max(m["n_halo"], 1), 0, 0, 0, self.mapped[p] + 4, 0, 0]
+        self.g_desc = torch.tensor(words, dtype=torch.int64, device=dev)
+        tgt = torch.cat([halo.send[p] for p in halo.peers_out])
+        src_peer = torch.cat([torch.full((halo.send_counts[p],), index_of[p], dtype=torch.int32, device=dev) for p in halo.peers_out])
+        src_elem = torch.cat([metas[p]["recv_offsets"][halo.rank] + torch.arange(halo.send_counts[p], device=dev)
+                              for p in halo.peers_out])
+        order = torch.sort(tgt, stable=True).indices            # by target; neighbours stay in ascending order
+        tgt, self.src_peer, self.src_elem = tgt[order], src_peer[order].contiguous(), src_elem[order].contiguous()
+        self.targets, counts = torch.unique_consecutive(tgt, return_counts=True)
+        self.target_ptr = torch.zeros(self.targets.numel() + 1, dtype=torch.int64, device=dev)
+        self.target_ptr[1:] = torch.cumsum(counts, 0)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)
+
+    def _p(self, t):
+        return self._c.c_void_p(t.data_ptr())
+
+    def _stream(self):
+        return self._c.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def extend(self, x_local):
+        """``[x_local | rows fetched from their owners]``: the forward exchange."""
+        halo, c = self.halo, self._c
+        x_local = x_local.contiguous()
+        x_ext = torch.empty((halo.n_local + halo.n_halo, self.width), dtype=x_local.dtype, device=x_local.device)
+        main, side = torch.cuda.current_stream(), self._side_stream()
+        side.wait_stream(main)
+        with torch.cuda.stream(side):                       # the local part is copied beside the exchange
+            x_ext.record_stream(side)
+            x_ext[:halo.n_local].copy_(x_local)
+        call = self._cabi.call
+        call("nb200_halo_publish", halo.n_local * self.width, self._p(x_local), None, c.c_void_p(self.base + self.x_off),
+             c.c_void_p(self.base), self._p(self.step_word), 1, self._p(self.arrivals), self.code, self._stream())
+        call("nb200_halo_pull_rows", len(halo.peers_in), self._p(self.x_desc), self._p(self.row_of_slot), self.x_largest,
+             self.row_bytes, self._p(x_ext), self._p(self.step_word), self._p(self.status), self.wait_budget_cycles,
+             self._stream())
+        main.wait_stream(side)
+        return x_ext
+
+    def reduce(self, g_ext):
+        """The local block of the gradient: ``g_ext[:n_local]`` plus the partial rows that the neighbours
+        computed for it (the backward exchange)."""
+        halo, c = self.halo, self._c
+        g_ext = g_ext.contiguous()
+        main, side = torch.cuda.current_stream(), self._side_stream()
+        side.wait_stream(main)
+        with torch.cuda.stream(side):                       # copied beside the publication of the halo part
+            g_local = g_ext[:halo.n_local].clone()
+        call = self._cabi.call
+        halo_part = c.c_void_p(g_ext.data_ptr() + halo.n_local * self.row_bytes)
+        call("nb200_halo_publish", halo.n_halo * self.width, halo_part, None, c.c_void_p(self.base + self.g_off),
+             c.c_void_p(self.base + 4), self._p(self.step_word), 0, self._p(self.arrivals), self.code, self._stream())
+        main.wait_stream(side)
+        g_local.record_stream(main)
+        call("nb200_halo_pull_add_rows", len(halo.peers_out), self._p(self.g_desc), int(self.targets.numel()),
+             self._p(self.targets), self._p(self.target_ptr), self._p(self.src_peer), self._p(self.src_elem), self.row_bytes,
+             self._p(g_local), self._p(self.step_word), self._p(self.status), self.wait_budget_cycles, self.code,
+             self._stream())
+        return g_local
+
+    def _side_stream(self):
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        return self._side
+
+    def check(self):
+        """Raise if a bounded wait of an exchange ran out (reads the status word: synchronises)."""
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise RuntimeError(f"peer-memory row exchange gave up waiting for a neighbour (status {code})")
+
+    def close(self):
+        lib = self._cabi.lib()
+        for ptr in self.mapped.values():
+            lib.nb200_ipc_close(self._c.c_void_p(ptr))
+        self.mapped = {}
+        if self.base is not None:
+            lib.nb200_ipc_free(self._c.c_void_p(self.base))
+            self.base = None
+
+
+def _row_exchange(A, x_local):
+    """The ``PeerRowExchange`` of A's halo plan for operands like ``x_local``, created (collectively) on
+    first use, or None when the send/recv path is to be used: CPU tensors, one rank, vectors, the
+    environment variable NB200_EXCHANGE=nccl, or a set-up that did not succeed on every rank."""
+    halo = A.halo
+    if not x_local.is_cuda or x_local.ndim != 2 or halo.world < 2 or os.environ.get("NB200_EXCHANGE", "auto") == "nccl":
+        return None
+    cache = halo.__dict__.setdefault("_row_exchanges", {})
+    key = (x_local.dtype, int(x_local.shape[1]))
+    if key not in cache:
+        for old in cache.values():                       # one set of buffers at a time
+            if old is not None and old.usable:
+                torch.cuda.synchronize(x_local.device)
+                dist.barrier(group=halo.group)
+                old.close()
+        cache.clear()
+        ex = PeerRowExchange(halo, x_local.dtype, int(x_local.shape[1]), x_local.device)
+        cache[key] = ex if ex.usable else None
+    return cache[key]
+
+
 class DistSpMVEngine:
     """Forward + backward of a row-partitioned SpMV as a fixed schedule of C-ABI launches over
     preallocated buffers, with the halo exchange overlapped with the rows that do not need it.
@@ -843,6 +1031,37 @@ class DistSpMVEngine:
             self.step()
         self._graph = graph
         return graph.replay
+
+    def phase_times(self, reps=50):
+        """Microseconds per call of the forward half alone and of the whole step, each replayed ``reps`` times
+        as a CUDA graph and timed with CUDA events on this rank; the backward half is their difference.
+        Collective: every rank must call it at the same point, after ``set_inputs``."""
+        def replayed(fn):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    fn()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn()
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            if dist.is_initialized():
+                dist.barrier(group=self.A.halo.group)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record()
+            e1.synchronize()
+            return e0.elapsed_time(e1) * 1e3 / reps
+        forward_us = replayed(self.forward)
+        step_us = replayed(self.step)
+        return {"forward_us": forward_us, "backward_us": step_us - forward_us, "step_us": step_us}
 
     def backward(self, g):
         """grad_A (pattern of the local rows) and grad_x (local block) for upstream gradient g;

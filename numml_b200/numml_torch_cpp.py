@@ -402,10 +402,10 @@ def spgemm_backward(grad_C, C_indices, C_indptr, A_rows, A_cols, A_data, A_indic
 sptrsv_wait_budget_cycles = 2_000_000_000
 _RESIDENT_THREADS = 148 * 2048               # threads a B200 keeps resident at once
 sptrsv_check_status = True
-# Which solve kernel runs: "auto" takes the cluster kernel (levels one after the other inside one
-# thread-block cluster, unknowns exchanged through distributed shared memory) for patterns with narrow
-# dependency levels and the grid-wide sync-free kernel otherwise; "syncfree" / "cluster" force one of
-# them ("cluster" still falls back when the ring of recent rows cannot fit).  Results are identical.
+# Which solve kernel runs: "auto" and "syncfree" take the grid-wide sync-free kernel; "cluster" takes the
+# cluster kernel (levels one after the other inside one thread-block cluster, unknowns exchanged through
+# distributed shared memory) whenever its ring of recent rows fits.  Results are identical; on B200 the
+# cluster barrier costs more per level than a store and a poll through L2, so "auto" never picks it.
 sptrsv_kernel = "auto"
 sptrsv_cluster_ctas = 8
 
@@ -433,34 +433,27 @@ def _team_lanes(n, nlevels):
     return lanes
 
 
-def _cluster_solve_fits(levels, n, nrhs, forced=False):
-    """Whether the cluster solve is taken for this pattern and number of right-hand sides: its ring must
-    hold `reach` rows of nrhs doubles within 200 KiB per CTA, the mean level must fit into two rounds of the
-    cluster's teams (wider levels keep the whole GPU busy with the sync-free kernel), and rows must be short
-    (the first eight entries of a row are prefetched, the rest is read on the critical path)."""
+def _cluster_solve_fits(levels, n, nrhs):
+    """Whether the cluster solve can run for this pattern and number of right-hand sides: its ring must
+    hold `reach` rows of nrhs doubles within 200 KiB per CTA."""
     if levels is None or nrhs < 1:
         return False
-    ctas = sptrsv_cluster_ctas
     cap = 1
-    while ctas * cap < levels["reach"]:
+    while sptrsv_cluster_ctas * cap < levels["reach"]:
         cap *= 2
-    lanes = 1
-    while lanes < 32 and lanes < nrhs:
-        lanes *= 2
-    teams = ctas * 512 // lanes
-    if cap * nrhs * 8 > 200 * 1024:
-        return False
-    return forced or (n <= 2 * teams * levels["nlevels"] and levels["longest_row"] <= 32)
+    return cap * nrhs * 8 <= 200 * 1024
 
 
-def _solve(plan, data, idx, ptr, perm, itype, order, nlevels, lower, unit, b, transposed=False):
+def _solve(plan, data, idx, ptr, perm, itype, lower, unit, b, transposed=False):
+    """x = A^{-1} b with the kernel named by ``sptrsv_kernel``."""
     n = plan.rows
     nrhs = 1 if b.ndim == 1 else int(b.shape[1])
     dev = b.device
     x = torch.empty_like(b)
-    if sptrsv_kernel in ("auto", "cluster") and n > 0 and nrhs > 0:
+    order, nlevels = plan.sptrsv_order(lower, transposed)
+    if sptrsv_kernel == "cluster" and n > 0 and nrhs > 0:
         levels = plan.sptrsv_level_plan(lower, transposed)
-        if _cluster_solve_fits(levels, n, nrhs, forced=sptrsv_kernel == "cluster"):
+        if _cluster_solve_fits(levels, n, nrhs):
             wbytes = _cabi.lib().nb200_sptrsv_solve_levels_workspace_bytes(n, nrhs, levels["entries"])
             work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
             _cabi.call("nb200_sptrsv_solve_levels", n, nrhs, levels["entries"], _ptr(data), _ptr(levels["src"]),
@@ -495,8 +488,7 @@ def sptrsv_forward(A_rows, A_cols, A_data, A_indices, A_indptr, lower, unit, b):
     plan.require(sorted_columns=True, diagonal=not unit, what="the triangular solve")
     idx, ptr, itype = plan.csr()
     with _on(dev):
-        order, nlevels = plan.sptrsv_order(lower)
-        return _solve(plan, A_data, idx, ptr, None, itype, order, nlevels, lower, unit, b)
+        return _solve(plan, A_data, idx, ptr, None, itype, lower, unit, b)
 
 
 def sptrsv_backward(grad_x, x, A_rows, A_cols, A_data, A_indices, A_indptr, lower, unit, b):
@@ -510,10 +502,8 @@ def sptrsv_backward(grad_x, x, A_rows, A_cols, A_data, A_indices, A_indptr, lowe
     nrhs = 1 if x.ndim == 1 else int(x.shape[1])
     with _on(dev):
         t_indptr, t_indices, t_perm, _ = plan.transpose()
-        order_t, nlevels_t = plan.sptrsv_order(not lower, transposed=True)
         # grad_b = A^{-T} grad_x: the opposite-triangle solve on the transposed structure
-        grad_b = _solve(plan, A_data, t_indices, t_indptr, t_perm, itype, order_t, nlevels_t, not lower, unit, grad_x,
-                        transposed=True)
+        grad_b = _solve(plan, A_data, t_indices, t_indptr, t_perm, itype, not lower, unit, grad_x, transposed=True)
         grad_A = torch.empty_like(A_data)
         _cabi.call("nb200_masked_outer", A_rows, plan.nnz, nrhs, _ptr(idx), _ptr(ptr), _ptr(grad_b), _ptr(x), -1.0,
                    _ptr(grad_A), _dtype_code(A_data), itype, _stream())

@@ -79,6 +79,27 @@ def _worker(rank, world, init_file):
             eng.close()
         # both exchanges add the neighbours' partial sums in the same order
         assert torch.equal(results["nccl"], results["peer"])
+        # SpMM: rows of the dense operand gathered from the neighbour's memory (forward) and partial gradient
+        # rows added by their owners (backward) equal the send/recv path bit for bit, and the oracle
+        X, G = W.randn((n, 6), 3, torch.float64), W.randn((m, 6), 4, torch.float64)
+        Y_ref = oracle.spdmm_forward(m, n, d, i, p, X)
+        gA2_ref, gX_ref = oracle.spdmm_backward(m, n, d, i, p, X, G)
+        got = {}
+        for exchange in ("nccl", "peer", "peer"):              # twice: both halves of the buffers
+            os.environ["NB200_EXCHANGE"] = "nccl" if exchange == "nccl" else "auto"
+            A.data.grad = None
+            Xl = X[lo:hi].to(dev).requires_grad_(True)
+            Y = A @ Xl
+            Y.backward(G[lo:hi].to(dev))
+            assert torch.equal(Y.detach().cpu(), Y_ref[lo:hi])
+            assert torch.allclose(A.data.grad.cpu(), gA2_ref[sl], rtol=1e-13, atol=1e-13)
+            assert torch.allclose(Xl.grad.cpu(), gX_ref[lo:hi], rtol=1e-13, atol=1e-13)
+            got[exchange] = (A.data.grad.clone(), Xl.grad.clone())
+        rows = A.halo._row_exchanges[(torch.float64, 6)]
+        assert rows is not None and rows.usable
+        rows.check()
+        assert torch.equal(got["nccl"][0], got["peer"][0]) and torch.equal(got["nccl"][1], got["peer"][1])
+        os.environ.pop("NB200_EXCHANGE", None)
         Cd, Ci, Cp = A @ A
         C_ref = oracle.spgemm_forward(m, n, d, i, p, m, n, d, i, p)
         assert torch.equal(Cp.cpu(), C_ref[2][lo:hi + 1] - C_ref[2][lo])

@@ -81,3 +81,56 @@ def test_wait_budget_runs_out_cleanly():
     torch.cuda.synchronize()
     assert int(status.item()) == ERR_WAIT_BUDGET and torch.all(grad == 1.0)
     assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0      # the device still answers
+
+
+@pytest.mark.parametrize("dtype,code,width", [(torch.float64, _cabi.F64, 6), (torch.float32, _cabi.F32, 128)])
+def test_rows_publish_pull_and_pull_add(dtype, code, width):
+    """Rows of a dense operand: the neighbour publishes its whole block, this rank gathers the rows it needs by
+    index; partial gradient rows are added to their targets in the listed order.  Three steps reuse both halves."""
+    dev = "cuda"
+    n_peer, n_halo, n_local = 500, 220, 400
+    es = torch.empty(0, dtype=dtype).element_size()
+    row_bytes = width * es
+    buf = torch.zeros(256 + 2 * n_peer * row_bytes + 2 * n_halo * row_bytes, dtype=torch.uint8, device=dev)
+    x_area, g_area = buf.data_ptr() + 256, buf.data_ptr() + 256 + 2 * n_peer * row_bytes
+    step = torch.zeros(1, dtype=torch.int32, device=dev)
+    arrivals = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    row_of_slot = torch.cat((torch.zeros(7, dtype=torch.int64, device=dev),          # slots of another neighbour
+                             torch.sort(torch.randperm(n_peer, device=dev)[:n_halo]).values)).contiguous()
+    x_desc = torch.tensor([x_area, n_peer, 7, n_halo, n_local, buf.data_ptr(), 0, 0], dtype=torch.int64, device=dev)
+    g_desc = torch.tensor([g_area, n_halo, 0, 0, 0, buf.data_ptr() + 4, 0, 0], dtype=torch.int64, device=dev)
+    targets = torch.sort(torch.randperm(n_local, device=dev)[:110]).values.contiguous()
+    tptr = (2 * torch.arange(111, device=dev)).contiguous()
+    src_peer = torch.zeros(220, dtype=torch.int32, device=dev)
+    src_elem = torch.randperm(n_halo, device=dev).contiguous()
+    for t in (1, 2, 3):
+        block = torch.randn((n_peer, width), dtype=dtype, device=dev)
+        _cabi.call("nb200_halo_publish", n_peer * width, P(block), None, ctypes.c_void_p(x_area), P(buf), P(step), 1,
+                   P(arrivals), code, _stream())
+        x_ext = torch.full((n_local + n_halo + 3, width), -7.0, dtype=dtype, device=dev)
+        _cabi.call("nb200_halo_pull_rows", 1, P(x_desc), P(row_of_slot), n_halo, row_bytes, P(x_ext), P(step), P(status),
+                   0, _stream())
+        assert int(step.item()) == t
+        assert torch.equal(x_ext[n_local:n_local + n_halo], block[row_of_slot[7:]])
+        assert torch.all(x_ext[:n_local] == -7.0) and torch.all(x_ext[n_local + n_halo:] == -7.0)
+        part = torch.randn((n_halo, width), dtype=dtype, device=dev)
+        _cabi.call("nb200_halo_publish", n_halo * width, P(part), None, ctypes.c_void_p(g_area),
+                   ctypes.c_void_p(buf.data_ptr() + 4), P(step), 0, P(arrivals), code, _stream())
+        grad = torch.randn((n_local, width), dtype=dtype, device=dev)
+        expect = grad.clone()
+        expect[targets] = (grad[targets] + part[src_elem[0::2]]) + part[src_elem[1::2]]
+        _cabi.call("nb200_halo_pull_add_rows", 1, P(g_desc), 110, P(targets), P(tptr), P(src_peer), P(src_elem), row_bytes,
+                   P(grad), P(step), P(status), 0, code, _stream())
+        assert torch.equal(grad, expect)
+    assert int(status.item()) == 0 and int(arrivals.item()) == 0
+    # a flag that nothing sets: the row kernels give up and leave their outputs alone
+    step.fill_(9)
+    x_ext = torch.full((n_local + n_halo, width), -1.0, dtype=dtype, device=dev)
+    _cabi.call("nb200_halo_pull_rows", 1, P(x_desc), P(row_of_slot), n_halo, row_bytes, P(x_ext), P(step), P(status),
+               2_000_000, _stream())
+    torch.cuda.synchronize()
+    assert int(status.item()) == ERR_WAIT_BUDGET and torch.all(x_ext == -1.0)
+    # a row that is not a multiple of 16 bytes is refused
+    with pytest.raises(RuntimeError):
+        _cabi.call("nb200_halo_pull_rows", 1, P(x_desc), P(row_of_slot), n_halo, 24, P(x_ext), P(step), P(status), 0, _stream())

@@ -12,10 +12,10 @@ from numml_b200 import workloads as W
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["syncfree", "cluster", "auto"])
+@pytest.fixture(params=["auto", "cluster"])
 def ops(request):
-    """The operator shim with the solve kernel forced to the grid-wide sync-free one, to the cluster
-    kernel (taken whenever its ring of recent rows fits), or left to choose."""
+    """The operator shim with its default solve kernel (grid-wide, sync-free) and with the optional cluster
+    kernel (taken whenever its ring of recent rows fits)."""
     from numml_b200 import numml_torch_cpp
     before = numml_torch_cpp.sptrsv_kernel
     numml_torch_cpp.sptrsv_kernel = request.param
