@@ -67,8 +67,16 @@ halo_publish_kernel(int64_t count, const T* __restrict__ src, const int64_t* __r
     const int t = *step_word + (bump ? 1 : 0);
     T* dst = area + (size_t)(t & 1) * (size_t)count;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < count; k += stride)
-        dst[k] = src[idx ? idx[k] : k];
+    if (!idx && ((count * sizeof(T)) & 15) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+        // a straight copy (the block of rows of a dense operand): 16 bytes per access
+        const uint4* s16 = reinterpret_cast<const uint4*>(src);
+        uint4* d16 = reinterpret_cast<uint4*>(dst);
+        const int64_t units = (int64_t)(count * sizeof(T) / 16);
+        for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < units; k += stride) d16[k] = s16[k];
+    } else {
+        for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < count; k += stride)
+            dst[k] = src[idx ? idx[k] : k];
+    }
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0 && atomicAdd(arrivals, 1u) == gridDim.x - 1) {
@@ -152,22 +160,26 @@ halo_pull_rows_kernel(const int64_t* __restrict__ desc, const int64_t* __restric
     const uint4* half = reinterpret_cast<const uint4*>(d[0]) + (size_t)(t & 1) * (size_t)d[1] * (size_t)w16;
     const int64_t* rows = row_of_slot + d[2];
     uint4* dst = dst_base + (size_t)d[4] * (size_t)w16;
-    const int64_t units = d[3] * w16, stride = (int64_t)gridDim.x * blockDim.x;
-    constexpr int U = 4;                                        // remote loads in flight per thread
-    for (int64_t k0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k0 < units; k0 += U * stride) {
-        uint4 v[U];
+    // a warp per row (no index arithmetic per unit), four rows in flight per warp
+    const int lane = threadIdx.x & 31;
+    const int64_t nslots = d[3];
+    const int64_t warps = (int64_t)gridDim.x * (kHaloThreads / 32);
+    constexpr int U = 4;
+    for (int64_t h0 = (int64_t)blockIdx.x * (kHaloThreads / 32) + (threadIdx.x >> 5); h0 < nslots; h0 += U * warps) {
+        const uint4* from[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int64_t k = k0 + u * stride;
-            if (k < units) {
-                const int64_t h = k / w16, c = k - h * w16;
-                v[u] = ld_fresh(half + rows[h] * w16 + c);
-            }
+            const int64_t h = h0 + u * warps;
+            from[u] = h < nslots ? half + rows[h] * w16 : nullptr;
         }
+        for (int64_t c = lane; c < w16; c += 32) {
+            uint4 v[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t k = k0 + u * stride;
-            if (k < units) dst[k] = v[u];
+            for (int u = 0; u < U; ++u)
+                if (from[u]) v[u] = ld_fresh(from[u] + c);
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (from[u]) dst[(h0 + u * warps) * w16 + c] = v[u];
         }
     }
 }
@@ -211,17 +223,20 @@ halo_pull_add_rows_kernel(int npeers, const int64_t* __restrict__ desc, int64_t 
     }
     __syncthreads();
     if (!ready) return;
-    const int64_t units = ntargets * w16, stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < units; k += stride) {
-        const int64_t j = k / w16, c = k - j * w16;
-        uint4* home = grad + target[j] * w16 + c;
-        uint4 acc = *home;
-        for (int64_t q = target_ptr[j]; q < target_ptr[j + 1]; ++q) {
-            const int64_t* d = desc + (int64_t)source_peer[q] * kHaloDescWords;
-            const uint4* half = reinterpret_cast<const uint4*>(d[0]) + (size_t)(t & 1) * (size_t)d[1] * (size_t)w16;
-            acc = Unit16<T>::add(acc, ld_fresh(half + source_elem[q] * w16 + c));
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (kHaloThreads / 32);
+    for (int64_t j = (int64_t)blockIdx.x * (kHaloThreads / 32) + (threadIdx.x >> 5); j < ntargets; j += warps) {
+        const int64_t q0 = target_ptr[j], q1 = target_ptr[j + 1];
+        uint4* home = grad + target[j] * w16;
+        for (int64_t c = lane; c < w16; c += 32) {
+            uint4 acc = home[c];
+            for (int64_t q = q0; q < q1; ++q) {                          // neighbours in ascending order
+                const int64_t* d = desc + (int64_t)source_peer[q] * kHaloDescWords;
+                const uint4* half = reinterpret_cast<const uint4*>(d[0]) + (size_t)(t & 1) * (size_t)d[1] * (size_t)w16;
+                acc = Unit16<T>::add(acc, ld_fresh(half + source_elem[q] * w16 + c));
+            }
+            home[c] = acc;
         }
-        *home = acc;
     }
 }
 
@@ -281,7 +296,7 @@ extern "C" int nb200_halo_pull_rows(int npeers, const int64_t* desc, const int64
     const int64_t w16 = row_bytes / 16;
     int per_peer = (kSMs * 8) / npeers;
     if (per_peer < 8) per_peer = 8;
-    const dim3 grid(halo_grid(largest_segment * w16, per_peer), (unsigned)npeers);
+    const dim3 grid(halo_grid(largest_segment * 32, per_peer), (unsigned)npeers);
     const long long budget = wait_budget_cycles > 0 ? wait_budget_cycles : 4000000000LL;
     halo_pull_rows_kernel<<<grid, kHaloThreads, 0, as_stream(stream)>>>(desc, row_of_slot, w16, (uint4*)dst, step_word,
                                                                        status, budget);
@@ -300,7 +315,7 @@ extern "C" int nb200_halo_pull_add_rows(int npeers, const int64_t* desc, int64_t
     const long long budget = wait_budget_cycles > 0 ? wait_budget_cycles : 4000000000LL;
     cudaStream_t st = as_stream(stream);
     return NB200_DISPATCH_T(dtype,
-        (halo_pull_add_rows_kernel<T><<<halo_grid(ntargets * w16, kSMs * 8), kHaloThreads, 0, st>>>(
+        (halo_pull_add_rows_kernel<T><<<halo_grid(ntargets * 32, kSMs * 8), kHaloThreads, 0, st>>>(
              npeers, desc, ntargets, target, target_ptr, source_peer, source_elem, w16, (uint4*)grad, step_word, status, budget),
          launch_status()));
 }
