@@ -904,7 +904,12 @@ class DistSpMVEngine:
             self._fwd_ops.append(dist.P2POp(dist.irecv, self.x_ext[o:o + halo.recv_counts[p]], halo._peer(p), group=halo.group))
         fw = lambda lo, hi: self._fwd_call(lo, hi, self.ptr, self.idx, None, self.x_ext, self.y, self.n_ext, self.br)  # noqa: E731
         self._fwd_interior = fw(a, b)
-        self._fwd_boundary = [c for c in (fw(0, a), fw(b, self.n)) if c is not None]
+        # With the peer exchange the boundary rows run beside the interior rows on a side stream.  The pipelined
+        # kernel of the interior rows fills every SM's shared memory, so a second pipelined kernel would only start
+        # when the first has drained; the register-staged kernel (hint 0) needs none and fits in beside it.
+        small = (lambda lo, hi: self._fwd_call(lo, hi, self.ptr, self.idx, None, self.x_ext, self.y, self.n_ext, 0)) \
+            if self.peer is not None else fw
+        self._fwd_boundary = [c for c in (small(0, a), small(b, self.n)) if c is not None]
         tp = lambda lo, hi: self._fwd_call(lo, hi, self.t_indptr, self.t_indices, self.t_perm, g, self.gx_ext, self.n, self.tbr)  # noqa: E731
         self._t_halo = tp(nl, self.n_ext)
         self._t_local = tp(0, nl)
@@ -927,6 +932,10 @@ class DistSpMVEngine:
             self.values_symmetric = self._local_values_symmetric()
             self._sym_ghost = sym(nl, self.n_ext) if self.n_ext > nl else None
             self._sym_local = sym(0, nl, int(self.values_symmetric))
+            # the same partial sums (row sums of the ghost rows, values through the mirror permutation, entries in
+            # storage order) from the register-staged forward kernel, which runs beside the local rows' pipelined one
+            self._ghost_light = self._fwd_call(nl, self.n_ext, self.ptr, self.idx, self.perm_ext, self.g_ext, self.gx_ext,
+                                               self.n_ext, 0) if self.peer is not None else None
         if self.peer is not None:
             self._peer_publish_x = self.peer.publish_x_args(self.x_ext)
             self._peer_pull_x = self.peer.pull_x_args(self.x_ext, self.status, self.wait_budget_cycles)
@@ -1083,7 +1092,10 @@ class DistSpMVEngine:
                 side.wait_stream(main)
                 with torch.cuda.stream(side):
                     s2 = self._c.c_void_p(side.cuda_stream)
-                    self._launch(lib.nb200_spgemv_backward_symmetric_rows, self._sym_ghost, s2)
+                    if self._ghost_light is not None:
+                        self._launch(lib.nb200_spgemv_forward, self._ghost_light, s2)
+                    else:
+                        self._launch(lib.nb200_spgemv_backward_symmetric_rows, self._sym_ghost, s2)
                     self._launch(lib.nb200_halo_publish, self._peer_publish_g, s2)
                 self._launch(lib.nb200_spgemv_backward_symmetric_rows, self._sym_local, stream)
                 main.wait_stream(side)
