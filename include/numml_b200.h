@@ -62,9 +62,12 @@ NB200_API const char* nb200_status_string(int status);
  * the row-streaming kernel (mean row length <= 24) the result is bit-identical to the reference
  * CPU loop.  `perm` (itype, may be NULL): when given, entry k uses data[perm[k]] -- this is how
  * a cached transposed structure is applied to the current values (y = A^T g).
- * `block_rows` selects the kernel: 0 = register-staged streaming (any matrix); R in 1..256 = the
- * persistent TMA-pipelined kernel, valid only if every block of R consecutive rows holds at most
- * nb200_spmv_pipeline_tile() entries (see nb200_csr_block_profile); the result is the same.
+ * `block_rows` selects the kernel: 0 = register-staged (row-streaming up to a mean row length of 24,
+ * a warp per row with a warp-reduced dot above it; any matrix); -1 = the row-streaming kernel whatever
+ * nnz / rows says (for a caller that passes a sub-range of rows: `indptr` offset by the first row, `y` likewise,
+ * `nnz` still the length of the arrays); R in 1..256 = the persistent TMA-pipelined kernel, valid only if every
+ * block of R consecutive rows holds at most nb200_spmv_pipeline_tile() entries (see nb200_csr_block_profile);
+ * the row-streaming and the pipelined kernel give the same bits.
  * `status` (device word, may be NULL) receives NB200_ERR_WAIT_BUDGET if a bounded wait of the
  * pipelined kernel ever runs out.
  * ------------------------------------------------------------------------------------------- */

@@ -259,8 +259,9 @@ int spmv_forward_launch(int64_t rows, int64_t nnz, const T* data, const I* indic
     if (block_rows > 0 && nnz > 0)
         return spmv_pipe_forward<T, I>(rows, nnz, block_rows, data, indices, indptr, perm, x, y, status, st);
     const double mean = (double)nnz / (double)rows;
-    if (mean <= kStreamMaxMeanRow) {
-        const int rpc = stream_rows_per_cta(rows, nnz);
+    if (mean <= kStreamMaxMeanRow || block_rows < 0) {
+        // block_rows < 0: the caller passes a sub-range of rows, for which nnz / rows says nothing
+        const int rpc = block_rows < 0 ? kStreamThreads : stream_rows_per_cta(rows, nnz);
         const int64_t grid = ceil_div(rows, (int64_t)rpc);
         if (grid > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;
         if (perm)
@@ -336,7 +337,7 @@ extern "C" int nb200_spgemv_forward(int64_t rows, int64_t cols, int64_t nnz,
                                     int dtype, int itype, nb200_stream stream) {
     if (rows < 0 || cols < 0 || nnz < 0) return NB200_ERR_BAD_ARG;
     if (rows == 0) return NB200_OK;
-    if (block_rows < 0 || block_rows > 256) return NB200_ERR_BAD_ARG;
+    if (block_rows < -1 || block_rows > 256) return NB200_ERR_BAD_ARG;
     if (!indptr || !y || (nnz > 0 && (!data || !indices || !x))) return NB200_ERR_BAD_ARG;
     if (!aligned16(data) || !aligned16(indices) || !aligned16(perm)) return NB200_ERR_ALIGN;
     if (itype == NB200_I32 && nnz > 0x7fffffffLL) return NB200_ERR_TOO_LARGE;

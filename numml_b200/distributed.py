@@ -886,7 +886,16 @@ class DistSpMVEngine:
             return None
         return [b - a, cols, int(idx.numel()), self._p(self.A.data), self._p(idx), self._p(ptr, a),
                 self._p(perm) if perm is not None else None, self._p(vec), self._p(out, a),
-                hint if a % 256 == 0 else 0, self._p(self.status), self.code, self.itype, None]
+                self._row_range_hint(a, b, int(ptr.numel()) - 1, hint), self._p(self.status), self.code, self.itype, None]
+
+    @staticmethod
+    def _row_range_hint(a, b, total_rows, hint):
+        """Kernel choice for rows [a, b): the pipelined kernel when the plan allows it and the range starts on one
+        of its row blocks; otherwise, for a proper sub-range, the row-streaming kernel named explicitly (-1),
+        because nnz / rows of a sub-range call says nothing about the rows in it."""
+        if hint > 0 and a % 256 == 0:
+            return hint
+        return 0 if (a == 0 and b == total_rows and hint >= 0) else -1
 
     def _prepare(self, g):
         """Everything that does not change from step to step: ctypes argument lists and the
@@ -907,7 +916,7 @@ class DistSpMVEngine:
         # With the peer exchange the boundary rows run beside the interior rows on a side stream.  The pipelined
         # kernel of the interior rows fills every SM's shared memory, so a second pipelined kernel would only start
         # when the first has drained; the register-staged kernel (hint 0) needs none and fits in beside it.
-        small = (lambda lo, hi: self._fwd_call(lo, hi, self.ptr, self.idx, None, self.x_ext, self.y, self.n_ext, 0)) \
+        small = (lambda lo, hi: self._fwd_call(lo, hi, self.ptr, self.idx, None, self.x_ext, self.y, self.n_ext, -1)) \
             if self.peer is not None else fw
         self._fwd_boundary = [c for c in (small(0, a), small(b, self.n)) if c is not None]
         tp = lambda lo, hi: self._fwd_call(lo, hi, self.t_indptr, self.t_indices, self.t_perm, g, self.gx_ext, self.n, self.tbr)  # noqa: E731
@@ -935,7 +944,7 @@ class DistSpMVEngine:
             # the same partial sums (row sums of the ghost rows, values through the mirror permutation, entries in
             # storage order) from the register-staged forward kernel, which runs beside the local rows' pipelined one
             self._ghost_light = self._fwd_call(nl, self.n_ext, self.ptr, self.idx, self.perm_ext, self.g_ext, self.gx_ext,
-                                               self.n_ext, 0) if self.peer is not None else None
+                                               self.n_ext, -1) if self.peer is not None else None
         if self.peer is not None:
             self._peer_publish_x = self.peer.publish_x_args(self.x_ext)
             self._peer_pull_x = self.peer.pull_x_args(self.x_ext, self.status, self.wait_budget_cycles)
