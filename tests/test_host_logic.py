@@ -120,3 +120,14 @@ def test_triangular_solve_team_size_follows_level_width():
     wide = ops._team_lanes(1 << 22, 100)                   # 42 k rows per level
     assert wide in (1, 2, 4, 8) and 42000 * wide <= 148 * 2048 < 42000 * wide * 2
     assert ops._team_lanes(5, 0) == 32                     # no levels recorded (empty matrix): harmless
+
+
+def test_row_range_hint_names_the_streaming_kernel_for_sub_ranges():
+    """A launch over a proper sub-range of rows must not let nnz / rows pick the kernel: it asks for the
+    row-streaming kernel (-1) unless the pipelined kernel applies (plan allows it, range starts on a block)."""
+    from numml_b200.distributed import DistSpMVEngine as E
+    assert E._row_range_hint(0, 100, 100, 0) == 0          # the whole matrix: the library chooses
+    assert E._row_range_hint(0, 50, 100, 0) == -1
+    assert E._row_range_hint(256, 512, 1000, 128) == 128
+    assert E._row_range_hint(100, 512, 1000, 128) == -1    # does not start on a row block
+    assert E._row_range_hint(0, 100, 100, -1) == -1
