@@ -77,7 +77,10 @@ halo_publish_kernel(int64_t count, const T* __restrict__ src, const int64_t* __r
         for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < count; k += stride)
             dst[k] = src[idx ? idx[k] : k];
     }
-    __threadfence_system();
+    // Device scope is enough here: the last block observes the other blocks' arrivals through the counter and its own
+    // system-scope fence below then orders everything they wrote before the flag (fences are cumulative); a
+    // system-scope fence in every thread costs several microseconds per launch.
+    __threadfence();
     __syncthreads();
     if (threadIdx.x == 0 && atomicAdd(arrivals, 1u) == gridDim.x - 1) {
         // last block: everything is packed and fenced; advance the step and raise the flag

@@ -526,8 +526,29 @@ class PeerExchange:
         src_peer = torch.cat([torch.full((halo.send_counts[p],), index_of[p], dtype=torch.int32, device=dev) for p in halo.peers_out])
         src_elem = torch.cat([metas[p]["g_segment"][halo.rank][0] + torch.arange(halo.send_counts[p], device=dev)
                               for p in halo.peers_out])
+        # the same sums through a local staging buffer: the neighbours' partial sums are copied over NVLink while
+        # the local rows are still being computed, and only a local addition is left for the end of the step
+        stage_off, off = {}, 0
+        for p in halo.peers_out:
+            stage_off[p] = off
+            off += halo.send_counts[p]
+        self.g_stage = torch.zeros(max(off, 1), dtype=dtype, device=dev)
+        words = []
+        for p in halo.peers_out:
+            m = metas[p]
+            seg_off, seg_cnt = m["g_segment"][halo.rank]
+            assert seg_cnt == halo.send_counts[p]
+            words += [self.mapped[p] + m["g_off"], m["n_halo"], seg_off, seg_cnt, stage_off[p], self.mapped[p] + 4, 0, 0]
+        self.g_pull_desc = torch.tensor(words, dtype=torch.int64, device=dev)
+        self.g_largest = max([halo.send_counts[p] for p in halo.peers_out], default=0)
+        # one descriptor that names the staging buffer as an "area" whose two halves coincide, flagged by this
+        # rank's own gradient flag (raised by its own publish of the same step)
+        self.stage_desc = torch.tensor([self.g_stage.data_ptr(), 0, 0, 0, 0, self.base + 4, 0, 0], dtype=torch.int64, device=dev)
+        stage_elem = torch.cat([stage_off[p] + torch.arange(halo.send_counts[p], device=dev) for p in halo.peers_out])
         order = torch.sort(tgt, stable=True).indices            # by target; neighbours stay in ascending order
         tgt, self.src_peer, self.src_elem = tgt[order], src_peer[order].contiguous(), src_elem[order].contiguous()
+        self.stage_elem = stage_elem[order].contiguous()
+        self.stage_peer = torch.zeros_like(self.src_peer)
         self.targets, counts = torch.unique_consecutive(tgt, return_counts=True)
         self.target_ptr = torch.zeros(self.targets.numel() + 1, dtype=torch.int64, device=dev)
         self.target_ptr[1:] = torch.cumsum(counts, 0)
@@ -536,6 +557,17 @@ class PeerExchange:
 
     def _p(self, t):
         return self._c.c_void_p(t.data_ptr())
+
+    def pull_g_args(self, status, budget):
+        """nb200_halo_pull of the neighbours' partial sums for this rank's columns into the staging buffer."""
+        return [len(self.halo.peers_out), self._p(self.g_pull_desc), self.g_largest, self._p(self.g_stage),
+                self._p(self.step_word), self._p(status), budget, self.code, None]
+
+    def add_g_args(self, grad_x, status, budget):
+        """nb200_halo_pull_add over the staging buffer: the same additions in the same order, all local."""
+        return [1, self._p(self.stage_desc), int(self.targets.numel()), self._p(self.targets), self._p(self.target_ptr),
+                self._p(self.stage_peer), self._p(self.stage_elem), self._p(grad_x), self._p(self.step_word), self._p(status),
+                budget, self.code, None]
 
     def publish_x_args(self, x_ext):
         """nb200_halo_publish: pack this rank's boundary entries of x and open a new step."""
@@ -842,9 +874,9 @@ class DistSpMVEngine:
             if peer.usable:
                 self.peer = peer
                 self.exchange = "peer memory: neighbours' packed values read over NVLink by this library's kernels, step flags with bounded waits"
-                self.schedule = ("[publish -> pull -> boundary rows || interior rows]; [ghost rows -> publish || local rows] -> pull-add"
-                                 " (two streams, no communication library in the step)")
-                self.launches_per_step = 4 + 4
+                self.schedule = ("[publish -> pull -> boundary rows || interior rows]; [ghost rows -> publish -> pull into a staging"
+                                 " buffer || local rows] -> local add (two streams, no communication library in the step)")
+                self.launches_per_step = 4 + 5
             elif self._exchange_request == "peer":
                 raise RuntimeError("the peer-memory exchange could not be set up on every rank")
         if self.br > 0 and self.n == halo.n_local and self.nnz > 0:
@@ -950,6 +982,8 @@ class DistSpMVEngine:
             self._peer_pull_x = self.peer.pull_x_args(self.x_ext, self.status, self.wait_budget_cycles)
             self._peer_publish_g = self.peer.publish_g_args(self.gx_ext)
             self._peer_pull_add = self.peer.pull_add_g_args(self.gx_ext, self.status, self.wait_budget_cycles)
+            self._peer_pull_g = self.peer.pull_g_args(self.status, self.wait_budget_cycles)
+            self._peer_add_g = self.peer.add_g_args(self.gx_ext, self.status, self.wait_budget_cycles)
 
     def _local_values_symmetric(self):
         """True if every local entry equals its mirror image bit for bit (entries in halo columns are
@@ -1106,8 +1140,11 @@ class DistSpMVEngine:
                     else:
                         self._launch(lib.nb200_spgemv_backward_symmetric_rows, self._sym_ghost, s2)
                     self._launch(lib.nb200_halo_publish, self._peer_publish_g, s2)
+                    self._launch(lib.nb200_halo_pull, self._peer_pull_g, s2)       # NVLink reads under the local rows
                 self._launch(lib.nb200_spgemv_backward_symmetric_rows, self._sym_local, stream)
                 main.wait_stream(side)
+                self._launch(lib.nb200_halo_pull_add, self._peer_add_g, stream)    # local additions only
+                return self.grad_A, self.grad_x
             else:
                 self._launch(lib.nb200_spgemv_forward, self._t_halo, stream)
                 self._launch(lib.nb200_halo_publish, self._peer_publish_g, stream)
