@@ -155,7 +155,6 @@ sptrsv_syncfree_kernel(int64_t n, int64_t nrhs, const T* __restrict__ data, cons
                 }
             }
             long long t0 = 0;
-            int next_d = 0;                                 // entries [0, next_d) of this group are already added
             for (unsigned spins = 0; pend != 0; ++spins) {
                 // Issue every outstanding poll before looking at any answer: the loads are then in
                 // flight together and one round costs one L2 round trip, not one per dependency.
@@ -173,18 +172,6 @@ sptrsv_syncfree_kernel(int64_t n, int64_t nrhs, const T* __restrict__ data, cons
                         pend &= ~(1u << d);
                     }
                 }
-                // Add what has arrived, in storage order, while the rest is still on its way: after the last
-                // arrival only the entries behind it remain between the poll and the division.
-#pragma unroll
-                for (int d = 0; d < D; ++d) {
-                    if (d == next_d && !((pend >> d) & 1u)) {
-                        if ((valid >> d) & 1u) {
-                            if (jj[d] == i) diag = aa[d];
-                            else acc = __dadd_rn(acc, __dmul_rn(aa[d], xv[d]));
-                        }
-                        next_d = d + 1;
-                    }
-                }
                 if (pend != 0) {
                     if (spins == 0) t0 = clock64();
                     if ((spins & 31u) == 31u) {
@@ -195,7 +182,7 @@ sptrsv_syncfree_kernel(int64_t n, int64_t nrhs, const T* __restrict__ data, cons
             }
 #pragma unroll
             for (int d = 0; d < D; ++d) {
-                if (d >= next_d && ((valid >> d) & 1u)) {
+                if ((valid >> d) & 1u) {
                     if (jj[d] == i) diag = aa[d];
                     else acc = __dadd_rn(acc, __dmul_rn(aa[d], xv[d]));
                 }
