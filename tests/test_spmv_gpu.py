@@ -290,6 +290,23 @@ def test_row_range_entry_points(oracle):
         assert_same(gx_ref, gx, f"grad_x (fused, two row ranges, values_symmetric={values_symmetric})")
     assert int(status.item()) == 0
 
+    # the forward on a short sub-range of rows (as the row-partitioned driver launches its boundary and ghost rows):
+    # block_rows = -1 names the row-streaming kernel, whose sums are the oracle's bit for bit; with 0 the library
+    # would go by nnz / rows, which for 300 of 8000 rows says "long rows" and picks the warp-per-row kernel
+    y_ref = oracle.spgemv_forward(m, k, d, i, p, x)
+    for lo, hi, perm in ((0, 300, None), (4099, 4400, None), (m - 257, m, None), (4099, 4400, t_perm)):
+        y = torch.full((m,), float("nan"), dtype=torch.float64, device="cuda")
+        ptr_lo = ctypes.c_void_p(ptr.data_ptr() + lo * ptr.element_size())
+        y_lo = ctypes.c_void_p(y.data_ptr() + lo * 8)
+        vals = dd if perm is None else d_sym.cuda()        # through the mirror permutation symmetric values are themselves
+        ref = y_ref if perm is None else oracle.spgemv_forward(m, k, d_sym, i, p, x)
+        _cabi.call("nb200_spgemv_forward", hi - lo, k, d.numel(), _cabi_ptr(vals), _cabi_ptr(idx), ptr_lo,
+                   _cabi_ptr(perm) if perm is not None else None, _cabi_ptr(dx), y_lo, -1, _cabi_ptr(status), _cabi.F64, itype, stream)
+        assert_same(ref[lo:hi], y[lo:hi], f"forward on rows [{lo}, {hi})")
+        assert torch.isnan(y[:lo]).all() and torch.isnan(y[hi:]).all()
+    assert _cabi.lib().nb200_spgemv_forward(m, k, d.numel(), _cabi_ptr(dd), _cabi_ptr(idx), _cabi_ptr(ptr), None, _cabi_ptr(dx),
+                                            _cabi_ptr(y), -2, None, _cabi.F64, itype, stream) == 1      # NB200_ERR_BAD_ARG
+
 
 @pytest.mark.parametrize("compiled", [True, False])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
