@@ -535,6 +535,10 @@ NB200_API int nb200_splu_numeric(int64_t n, void* Mt_data, const int64_t* Mt_ind
  *                      caller holding the number of the current step; with `bump_step` != 0 the call
  *                      first advances it by one (the first publish of a step does that).  `arrivals` is a
  *                      zeroed device word used to find the last block.
+ * nb200_halo_publish_rowsums   nb200_halo_publish whose values are computed on the way: element r is the row sum
+ *                      sum_k data[perm[k]] * x[indices[k]] over row r of (indptr, indices) (`perm` may be NULL),
+ *                      entries in storage order, unfused: the partial sums of grad_x owed to the neighbours, one row
+ *                      per halo column.  `indptr` points at the first of the `rows` rows (absolute entry positions).
  * nb200_halo_pull      for each of `npeers` neighbours, described by 8 int64 words each
  *                      ([0] address of its packed area, [1] elements per half, [2] first element of this
  *                      rank's segment, [3] elements in it, [4] first destination element in `dst`,
@@ -570,6 +574,9 @@ NB200_API int nb200_splu_numeric(int64_t n, void* Mt_data, const int64_t* Mt_ind
  * ------------------------------------------------------------------------------------------- */
 NB200_API int nb200_halo_publish(int64_t count, const void* src, const int64_t* idx, void* area, int32_t* flag,
                                  int32_t* step_word, int bump_step, uint32_t* arrivals, int dtype, nb200_stream stream);
+NB200_API int nb200_halo_publish_rowsums(int64_t rows, const void* data, const void* indices, const void* indptr,
+                                         const void* perm, const void* x, void* area, int32_t* flag, int32_t* step_word,
+                                         int bump_step, uint32_t* arrivals, int dtype, int itype, nb200_stream stream);
 NB200_API int nb200_halo_pull(int npeers, const int64_t* desc, int64_t largest_segment, void* dst,
                               const int32_t* step_word, int32_t* status, int64_t wait_budget_cycles,
                               int dtype, nb200_stream stream);

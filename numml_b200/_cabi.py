@@ -75,6 +75,7 @@ SIGNATURES = {
     "nb200_splu_symbolic_fill": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _int, _vp]),
     "nb200_splu_numeric": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp]),
     "nb200_halo_publish": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _int, _vp, _int, _vp]),
+    "nb200_halo_publish_rowsums": (_int, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp, _int, _int, _vp]),
     "nb200_halo_pull": (_int, [_int, _vp, _i64, _vp, _vp, _vp, _i64, _int, _vp]),
     "nb200_halo_pull_add": (_int, [_int, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp]),
     "nb200_halo_pull_rows": (_int, [_int, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),

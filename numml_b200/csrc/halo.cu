@@ -91,6 +91,36 @@ halo_publish_kernel(int64_t count, const T* __restrict__ src, const int64_t* __r
     }
 }
 
+// publish with the values computed on the way: element r of the packed area is the row sum
+// sum_k data[perm[k]] * x[indices[k]] over row r of (indptr, indices), entries in storage order, unfused -- the
+// partial sums of grad_x that a rank owes its neighbours, one row per halo column (the ghost rows of the
+// row-partitioned driver).  One launch instead of a row-sum kernel followed by a packing kernel.
+template <typename T, typename I>
+__global__ void __launch_bounds__(kHaloThreads)
+halo_publish_rowsums_kernel(int64_t rows, const T* __restrict__ data, const I* __restrict__ indices,
+                            const I* __restrict__ indptr, const I* __restrict__ perm, const T* __restrict__ x,
+                            T* area, int* flag, int* step_word, int bump, unsigned* arrivals) {
+    const int t = *step_word + (bump ? 1 : 0);
+    T* dst = area + (size_t)(t & 1) * (size_t)rows;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += stride) {
+        T acc = 0;
+        for (int64_t k = (int64_t)indptr[r]; k < (int64_t)indptr[r + 1]; ++k) {
+            const T a = perm ? data[(int64_t)perm[k]] : data[k];
+            acc = add_rn(acc, mul_rn(a, x[(int64_t)indices[k]]));
+        }
+        dst[r] = acc;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(arrivals, 1u) == gridDim.x - 1) {
+        *arrivals = 0;
+        if (bump) *step_word = t;
+        __threadfence_system();
+        st_release_sys(flag, t);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kHaloThreads)
 halo_pull_kernel(const int64_t* __restrict__ desc, T* dst_base, const int* step_word, int32_t* status, long long budget) {
@@ -260,6 +290,18 @@ extern "C" int nb200_halo_publish(int64_t count, const void* src, const int64_t*
     return NB200_DISPATCH_T(dtype,
         (halo_publish_kernel<T><<<grid, kHaloThreads, 0, st>>>(count, (const T*)src, idx, (T*)area, flag, step_word,
                                                                bump_step, arrivals), launch_status()));
+}
+
+extern "C" int nb200_halo_publish_rowsums(int64_t rows, const void* data, const void* indices, const void* indptr,
+                                          const void* perm, const void* x, void* area, int32_t* flag, int32_t* step_word,
+                                          int bump_step, uint32_t* arrivals, int dtype, int itype, nb200_stream stream) {
+    if (rows < 0 || !area || !flag || !step_word || !arrivals) return NB200_ERR_BAD_ARG;
+    if (rows > 0 && (!data || !indices || !indptr || !x)) return NB200_ERR_BAD_ARG;
+    cudaStream_t st = as_stream(stream);
+    const unsigned grid = halo_grid(rows, 64);
+    return NB200_DISPATCH(dtype, itype,
+        (halo_publish_rowsums_kernel<T, I><<<grid, kHaloThreads, 0, st>>>(rows, (const T*)data, (const I*)indices,
+             (const I*)indptr, (const I*)perm, (const T*)x, (T*)area, flag, step_word, bump_step, arrivals), launch_status()));
 }
 
 extern "C" int nb200_halo_pull(int npeers, const int64_t* desc, int64_t largest_segment, void* dst,

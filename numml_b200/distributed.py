@@ -832,6 +832,7 @@ class DistSpMVEngine:
         self._exchange_request = os.environ.get("NB200_EXCHANGE", exchange)
         self.use_value_symmetry = True
         self.values_symmetric = False
+        self.backward_schedule = os.environ.get("NB200_BACKWARD_SCHEDULE", "sequential")   # or "forked"
         self._side = None
         self.peer = None
         self.wait_budget_cycles = 4_000_000_000
@@ -984,6 +985,19 @@ class DistSpMVEngine:
             self._peer_pull_add = self.peer.pull_add_g_args(self.gx_ext, self.status, self.wait_budget_cycles)
             self._peer_pull_g = self.peer.pull_g_args(self.status, self.wait_budget_cycles)
             self._peer_add_g = self.peer.add_g_args(self.gx_ext, self.status, self.wait_budget_cycles)
+            if self.fused and self.n_ext > nl:
+                # ghost rows and publication in one launch: the row sums go straight into the exchange buffer
+                pk = self.peer
+                self._ghost_publish = [self.n_ext - nl, self._p(self.A.data), self._p(self.idx), self._p(self.ptr, nl),
+                                       self._p(self.perm_ext), self._p(self.g_ext), self._c.c_void_p(pk.base + pk.g_off),
+                                       self._c.c_void_p(pk.base + 4), self._p(pk.step_word), 0, self._p(pk.arrivals),
+                                       self.code, self.itype, None]
+                if self.backward_schedule == "sequential":
+                    self.schedule = ("[publish -> pull -> boundary rows || interior rows]; ghost rows + publish (one launch) -> local rows"
+                                     " -> pull-add over NVLink (no communication library in the step)")
+                    self.launches_per_step = 4 + 3
+            else:
+                self._ghost_publish = None
 
     def _local_values_symmetric(self):
         """True if every local entry equals its mirror image bit for bit (entries in halo columns are
@@ -1128,6 +1142,15 @@ class DistSpMVEngine:
         stream = self._c.c_void_p(torch.cuda.current_stream().cuda_stream)
         # partial sums for halo columns first, so that their exchange overlaps the rest
         if self.peer is not None:
+            if self.fused and self._ghost_publish is not None and self.backward_schedule == "sequential":
+                # The pipelined kernel of the local rows takes every register of every SM, so nothing launched beside
+                # it overlaps with it; the shortest chain is then: ghost rows + publication in one small launch, the
+                # local rows, and one launch that reads the neighbours' sums over NVLink (long published by then)
+                # and adds them.
+                self._launch(lib.nb200_halo_publish_rowsums, self._ghost_publish, stream)
+                self._launch(lib.nb200_spgemv_backward_symmetric_rows, self._sym_local, stream)
+                self._launch(lib.nb200_halo_pull_add, self._peer_pull_add, stream)
+                return self.grad_A, self.grad_x
             if self.fused:
                 # ghost rows and the publication of their partial sums run beside the local rows
                 main = torch.cuda.current_stream()

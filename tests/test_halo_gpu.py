@@ -134,3 +134,35 @@ def test_rows_publish_pull_and_pull_add(dtype, code, width):
     # a row that is not a multiple of 16 bytes is refused
     with pytest.raises(RuntimeError):
         _cabi.call("nb200_halo_pull_rows", 1, P(x_desc), P(row_of_slot), n_halo, 24, P(x_ext), P(step), P(status), 0, _stream())
+
+
+@pytest.mark.parametrize("dtype,code", [(torch.float64, _cabi.F64), (torch.float32, _cabi.F32)])
+def test_publish_rowsums_matches_row_sums_then_publish(dtype, code):
+    """The fused launch (row sums through a permutation, written straight into the packed area, flag raised) gives
+    the bits of the two-launch path: the row-streaming forward kernel over the same rows, then nb200_halo_publish."""
+    dev = "cuda"
+    from numml_b200 import workloads as W
+    d, i, p, (m, k) = W.random_csr(700, 900, 0.01, seed=5, dtype=dtype)
+    rows0 = 123                                           # the published rows are rows [rows0, m)
+    nrows = m - rows0
+    es = torch.empty(0, dtype=dtype).element_size()
+    perm = torch.randperm(d.numel())
+    dd, di, dp, dperm = d.cuda(), i.cuda().to(torch.int32), p.cuda().to(torch.int32), perm.cuda().to(torch.int32)
+    x = torch.randn(k, dtype=dtype, device=dev)
+    step = torch.zeros(1, dtype=torch.int32, device=dev)
+    arrivals = torch.zeros(1, dtype=torch.int32, device=dev)
+    ptr_lo = ctypes.c_void_p(dp.data_ptr() + rows0 * 4)
+    for t in (1, 2, 3):
+        buf = torch.zeros(256 + 2 * nrows * es, dtype=torch.uint8, device=dev)
+        area = ctypes.c_void_p(buf.data_ptr() + 256)
+        y = torch.empty(m, dtype=dtype, device=dev)
+        _cabi.call("nb200_spgemv_forward", nrows, k, d.numel(), P(dd), P(di), ptr_lo, P(dperm), P(x),
+                   ctypes.c_void_p(y.data_ptr() + rows0 * es), -1, None, code, _cabi.I32, _stream())
+        _cabi.call("nb200_halo_publish_rowsums", nrows, P(dd), P(di), ptr_lo, P(dperm), P(x), area, P(buf), P(step), 1,
+                   P(arrivals), code, _cabi.I32, _stream())
+        assert int(step.item()) == t and buf[:4].view(torch.int32).item() == t
+        half = buf[256:].view(dtype)[(t & 1) * nrows:(t & 1) * nrows + nrows]
+        assert torch.equal(half, y[rows0:])
+        other = buf[256:].view(dtype)[(1 - (t & 1)) * nrows:(1 - (t & 1)) * nrows + nrows]
+        assert torch.all(other == 0)
+    assert int(arrivals.item()) == 0
