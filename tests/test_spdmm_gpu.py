@@ -43,11 +43,26 @@ def test_random_vs_oracle(oracle, ops, dtype, K):
     assert_same(gB_ref, gB, "grad_B")
 
 
+def _rows_of_given_lengths(lengths, n, seed):
+    """CSR matrix whose row r has lengths[r] entries in sorted distinct random columns, N(0,1) values."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    cols = [np.sort(rng.choice(n, size=int(k), replace=False)) for k in lengths]
+    ptr = np.concatenate(([0], np.cumsum([len(c) for c in cols])))
+    idx = np.concatenate(cols) if ptr[-1] > 0 else np.zeros(0, dtype=np.int64)
+    dat = rng.standard_normal(int(ptr[-1])).astype(np.float32)
+    return torch.from_numpy(dat), torch.from_numpy(idx.astype(np.int64)), torch.from_numpy(ptr.astype(np.int64))
+
+
 def test_long_and_empty_rows(oracle, ops):
-    """Power-law rows (1 ... 700 entries) next to empty ones."""
+    """Power-law rows (1 ... 700 entries) next to empty ones, a random matrix with empty rows, and rows of 4096
+    and 5000 entries (the graph benchmark's longest rows and beyond) between empty and one-entry rows: the
+    degree-ordered row schedule and the lane-group walk of a long row give the oracle's bits."""
     d, i, p, (m, n) = W.powerlaw_graph(3000, scale=8, max_deg=700, seed=3, dtype=torch.float32)
     d2, i2, p2, _ = W.random_csr(m, n, 0.0005, seed=9, dtype=torch.float32)   # has empty rows
-    for (dat, idx, ptr) in ((d, i, p), (d2, i2, p2)):
+    lengths = [4096, 0, 5000, 1, 0, 700, 4096, 33, 0, 2] + [7] * 200 + [0, 4096] + [1] * 50
+    d3, i3, p3 = _rows_of_given_lengths(lengths, 6000, seed=11)
+    for (dat, idx, ptr, m, n) in ((d, i, p, m, n), (d2, i2, p2, m, n), (d3, i3, p3, len(lengths), 6000)):
         B, G = W.randn((n, 128), 1, torch.float32), W.randn((m, 128), 2, torch.float32)
         C_ref = oracle.spdmm_forward(m, n, dat, idx, ptr, B)
         gA_ref, gB_ref = oracle.spdmm_backward(m, n, dat, idx, ptr, B, G)
