@@ -324,6 +324,11 @@ def _header(work):
     return work[:192].view(torch.int64).cpu()
 
 
+# Whether the results of the symbolic phase of the most recent product are kept with the plan of its left factor
+# (about 40 bytes per row of A): a product of the same two patterns then runs its numeric phase only.
+spgemm_keep_symbolic = True
+
+
 def spgemm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B_rows, B_cols, B_data, B_indices, B_indptr):
     dev = _require_cuda(A_data, A_indices, A_indptr, B_data, B_indices, B_indptr)
     A_data = _values(A_data)
@@ -335,6 +340,23 @@ def spgemm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B_rows, B_cols, 
     vbytes = A_data.element_size()
     with _on(dev):
         wbytes = _cabi.lib().nb200_spgemm_workspace_bytes(A_rows)
+        # The symbolic phase depends on the two patterns only.  Its results (row pointers of C, the binned row
+        # lists the numeric phase walks, the size of its spill area) are kept with the plan of the left factor for
+        # the most recent right factor (from the second product of the pair on), so that a product of the same
+        # patterns with new values -- every step of a training loop -- runs the numeric phase alone, with no host
+        # read in between.
+        key = ("spgemm_symbolic", itype)
+        kept = plan_a.extra.get(key) if spgemm_keep_symbolic else None
+        if kept is not None and kept["plan_b"] is plan_b:
+            C_indptr = kept["C_indptr"].clone()
+            nnz_c, slots = kept["nnz"], kept["spill_slots"]
+            spill = torch.empty(slots * (vbytes + 4), dtype=torch.uint8, device=dev) if slots else None
+            C_indices = torch.empty(nnz_c, dtype=torch.int64, device=dev)
+            C_data = torch.empty(nnz_c, dtype=A_data.dtype, device=dev)
+            _cabi.call("nb200_spgemm_numeric", A_rows, A_cols, B_cols, _ptr(A_data), _ptr(ai), _ptr(ap),
+                       _ptr(B_data), _ptr(bi), _ptr(bp), code, itype, _ptr(kept["work"]), wbytes, _ptr(spill), slots,
+                       _ptr(C_indptr), _ptr(C_indices), _ptr(C_data), _stream())
+            return [C_data, C_indices, C_indptr]
         work = torch.empty(wbytes, dtype=torch.uint8, device=dev)
         C_indptr = torch.empty(A_rows + 1, dtype=torch.int64, device=dev)
 
@@ -364,6 +386,16 @@ def spgemm_forward(A_rows, A_cols, A_data, A_indices, A_indptr, B_rows, B_cols, 
         _cabi.call("nb200_spgemm_numeric", A_rows, A_cols, B_cols, _ptr(A_data), _ptr(ai), _ptr(ap),
                    _ptr(B_data), _ptr(bi), _ptr(bp), code, itype, _ptr(work), wbytes, _ptr(spill), slots,
                    _ptr(C_indptr), _ptr(C_indices), _ptr(C_data), _stream())
+        if spgemm_keep_symbolic:
+            # kept from the second product of a pair of patterns on: a product that is formed once (an intermediate
+            # of a chain with fresh operands) must not pin 40 bytes per row for the life of its plan
+            seen = ("spgemm_seen", itype)
+            if plan_a.extra.get(seen) is plan_b:
+                plan_a.extra[key] = {"plan_b": plan_b, "work": work, "C_indptr": C_indptr.clone(), "nnz": nnz_c,
+                                     "spill_slots": slots}
+            else:
+                plan_a.extra[seen] = plan_b
+                plan_a.extra.pop(key, None)
     return [C_data, C_indices, C_indptr]
 
 

@@ -174,3 +174,41 @@ def test_structure_properties_at_scale(ops):
     lhs = ops.spgemv_forward(m, m, Cd, Ci, Cp, ones)
     rhs = ops.spgemv_forward(m, m, *dA, ops.spgemv_forward(m, m, *dA, ones))
     assert torch.allclose(lhs, rhs, atol=1e-12)
+
+
+@pytest.mark.parametrize("case", ["stencil", "random"])
+def test_kept_symbolic_phase_gives_the_same_product(oracle, ops, case):
+    """A second product of the same two patterns with other values runs the numeric phase alone, on the row
+    pointers and row lists kept from the first: same structure, values as the oracle's, and the same bits as with
+    the keeping switched off.  The row pointers returned are a tensor of their own each time."""
+    if case == "stencil":
+        ad, ai, ap, (m, k) = W.poisson2d_5pt(96, torch.float64)
+        bd, bi, bp, (_, n) = ad.clone(), ai, ap, (m, k)
+    else:                                                   # long and short rows: hash bins and the spill path's header
+        ad, ai, ap, (m, k) = W.random_csr(300, 400, 0.05, seed=3, dtype=torch.float64)
+        bd, bi, bp, (_, n) = W.random_csr(400, 350, 0.08, seed=4, dtype=torch.float64)
+    dA_idx, dA_ptr, dB_idx, dB_ptr = ai.cuda(), ap.cuda(), bi.cuda(), bp.cuda()
+    assert ops.spgemm_keep_symbolic
+    outs = []
+    for rep, scale in enumerate((1.0, -0.75, 3.0, 0.5)):
+        a, b = ad * scale, bd + scale
+        ref = oracle.spgemm_forward(m, k, a, ai, ap, k, n, b, bi, bp)
+        Cd, Ci, Cp = ops.spgemm_forward(m, k, a.cuda(), dA_idx, dA_ptr, k, n, b.cuda(), dB_idx, dB_ptr)
+        assert_same(ref[2], Cp, "C_indptr")
+        assert_same(ref[1], Ci, "C_indices")
+        assert_close(ref[0], Cd, "C_data")
+        outs.append((Cd, Ci, Cp))
+        if rep > 0:                                         # kept from the second product of the pair on
+            from numml_b200 import _plan
+            kept = _plan.get_plan(m, k, dA_idx, dA_ptr).extra
+            assert any(isinstance(key, tuple) and key[0] == "spgemm_symbolic" for key in kept)
+            assert Cp.data_ptr() != outs[0][2].data_ptr()
+    ops.spgemm_keep_symbolic = False
+    try:
+        a, b = ad * 0.5, bd + 0.5
+        Cd, Ci, Cp = ops.spgemm_forward(m, k, a.cuda(), dA_idx, dA_ptr, k, n, b.cuda(), dB_idx, dB_ptr)
+    finally:
+        ops.spgemm_keep_symbolic = True
+    if case == "stencil":                                   # register-merge rows: values reproducible bit for bit
+        assert torch.equal(Cd, outs[3][0])
+    assert torch.equal(Ci, outs[3][1]) and torch.equal(Cp, outs[3][2])
